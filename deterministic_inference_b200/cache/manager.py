@@ -31,7 +31,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from ..parts.spec import PagedKVSpec, StateSpec
+from ..parts.spec import CompositeSpec, PagedKVSpec, StateSpec, flatten_cache_specs
 
 NULL_PAGE = 0
 
@@ -48,12 +48,15 @@ class OutOfPages(CacheError):
 class CacheView:
     """What a mixer sees of the one cache its schedule entry names."""
 
-    kv: Optional[torch.Tensor] = None            # [pages, 2, Hkv, page_size, D] of this cache
+    kv: Optional[torch.Tensor] = None            # [pages, 2, Hkv, page_size, D] of this cache; with
+                                                 # values of another size than keys [pages, Hkv *
+                                                 # page_size * (D + Dv)]: a page's keys, then its values
     page_size: int = 0
     slot_mapping: Optional[torch.Tensor] = None  # int32 [T]: page * page_size + offset
     attention_meta: object = None                # the group's AttentionMeta of this step
     state: Optional[torch.Tensor] = None         # [max_reqs, *shape] of this cache
     writes: bool = True
+    members: Optional[list] = None               # a composite cache: one view per inner mixer (or None)
 
 
 class PageGroup:
@@ -66,6 +69,8 @@ class PageGroup:
         self.key, self.spec, self.cache_ids = key, spec, list(cache_ids)
         self.num_pages, self.page_size = int(num_pages), int(page_size)
         self.window = spec.window
+        # with a window: pages that hold one of the first ``keep_first`` positions are never given back
+        self.keep_first = int(spec.keep_first) if spec.window is not None else 0
         # LIFO: pop() takes from the end; low page ids are handed out first at start
         self.free: list[int] = list(range(num_pages - 1, 0, -1))
         self.held: set[int] = set()
@@ -108,7 +113,8 @@ class PageGroup:
         first_needed = next_position - self.window + 1
         n = 0
         pl = self.pages[slot]
-        for i in range(len(pl)):
+        kept = -(-self.keep_first // self.page_size)     # pages that hold a kept position
+        for i in range(kept, len(pl)):
             if (i + 1) * self.page_size <= first_needed:
                 if pl[i] != NULL_PAGE:
                     self._give_back(pl[i])
@@ -139,12 +145,13 @@ def group_page_bytes(cache_specs: dict, page_size: int, dtype: torch.dtype) -> d
     of paged caches among ``cache_specs`` (cache id -> need)."""
     count: dict = {}
     specs: dict = {}
-    for spec in cache_specs.values():
+    for spec in flatten_cache_specs(cache_specs).values():
         if isinstance(spec, PagedKVSpec):
             count[spec.group_key()] = count.get(spec.group_key(), 0) + 1
             specs[spec.group_key()] = spec
     item = _element_size(dtype)
-    return {k: (specs[k], n * 2 * specs[k].num_kv_heads * page_size * specs[k].head_dim * item)
+    return {k: (specs[k], n * specs[k].num_kv_heads * page_size
+                * (specs[k].head_dim + specs[k].value_dim) * item)
             for k, n in count.items()}
 
 
@@ -161,7 +168,8 @@ def pages_for_budget(cache_specs: dict, byte_budget: int, page_size: int, dtype:
     cap = {}
     for k, (spec, _) in groups.items():
         if spec.window is not None:
-            cap[k] = 1 + max_reqs * (-(-(spec.window + step_tokens) // page_size) + 2)
+            cap[k] = 1 + max_reqs * (-(-(spec.window + step_tokens) // page_size) + 2
+                                     + -(-spec.keep_first // page_size))
     lo, hi = 2, max(2, byte_budget // min(b for _, b in groups.values()))
     def cost(n):
         return sum(min(n, cap.get(k, n)) * b for k, (_, b) in groups.items())
@@ -191,10 +199,12 @@ class CacheManager:
         self.state_groups: dict[tuple, StateGroup] = {}
         self._where: dict[int, tuple] = {}       # cache id -> (group, index in group)
 
-        by_key: dict[tuple, list[int]] = {}
+        by_key: dict[tuple, list] = {}
         specs: dict[tuple, object] = {}
-        for cid in sorted(cache_specs):
-            spec = cache_specs[cid]
+        # a composite cache's members live in the groups of their own kinds, under (id, member)
+        self._composite: dict[int, int] = {cid: len(spec.members) for cid, spec in cache_specs.items()
+                                           if isinstance(spec, CompositeSpec)}
+        for cid, spec in flatten_cache_specs(cache_specs).items():
             by_key.setdefault(spec.group_key(), []).append(cid)
             specs[spec.group_key()] = spec
         for key, cids in by_key.items():
@@ -223,13 +233,18 @@ class CacheManager:
     def bytes_per_page(self) -> int:
         """Bytes of one page over all groups and caches (for sizing the pool)."""
         item = _element_size(self.dtype)
-        return sum(len(g.cache_ids) * 2 * g.spec.num_kv_heads * g.page_size * g.spec.head_dim * item
-                   for g in self.page_groups.values())
+        return sum(len(g.cache_ids) * g.spec.num_kv_heads * g.page_size
+                   * (g.spec.head_dim + g.spec.value_dim) * item for g in self.page_groups.values())
 
     def allocate_device_memory(self) -> None:
         for g in self.page_groups.values():
-            g.pool = torch.zeros(len(g.cache_ids), g.num_pages, 2, g.spec.num_kv_heads, g.page_size,
-                                 g.spec.head_dim, dtype=self.dtype, device=self.device)
+            if g.spec.value_dim == g.spec.head_dim:
+                g.pool = torch.zeros(len(g.cache_ids), g.num_pages, 2, g.spec.num_kv_heads, g.page_size,
+                                     g.spec.head_dim, dtype=self.dtype, device=self.device)
+            else:     # a page: its keys [Hkv, page_size, D], then its values [Hkv, page_size, Dv]
+                g.pool = torch.zeros(len(g.cache_ids), g.num_pages, g.spec.num_kv_heads * g.page_size
+                                     * (g.spec.head_dim + g.spec.value_dim),
+                                     dtype=self.dtype, device=self.device)
         for g in self.state_groups.values():
             dt = getattr(torch, g.spec.dtype)
             g.array = torch.zeros(len(g.cache_ids), self.max_reqs, *g.spec.shape, dtype=dt,
@@ -339,7 +354,11 @@ class CacheManager:
     def group_of(self, cache_id: int):
         return self._where[cache_id][0]
 
-    def view(self, cache_id: int, step, writes: bool = True) -> CacheView:
+    def view(self, cache_id, step, writes: bool = True) -> CacheView:
+        if cache_id in self._composite:
+            return CacheView(writes=writes, members=[
+                self.view((cache_id, mi), step, writes) if (cache_id, mi) in self._where else None
+                for mi in range(self._composite[cache_id])])
         g, i = self._where[cache_id]
         if isinstance(g, PageGroup):
             gb = step.groups[g.key]

@@ -1,0 +1,214 @@
+// Generalised delta rule with a decay per key channel: per head a state S [D keys, D values]
+// in float32, carried from token to token in the request's state slot,
+//   S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T,   o_t = S_t^T r_t,
+// with u = k / sqrt(sum(k^2) + key_eps) the unit key, w = exp(-decay_scale * sigmoid(lora + w0))
+// the decay and a = sigmoid(. + bias) the removal rate.  Three kernels: the per-token vectors
+// (all float32), the recurrence, and the output (per-head RMS norm, weight, sigmoid gate).
+#include <cuda_pipeline.h>
+
+#include "source.cuh"
+
+// proj row: [r | k | v | g | a_pre | lora hidden] = 5 * H * D + R columns.
+// packed [T][H][6][D] float32: w, a * u, u, k, r, v.
+__global__ void delta_prepare_kernel(Source proj, const void* w2, int w_dtype, const float* w0,
+                                     const float* a_bias, float* packed, int H, int D, int R,
+                                     float decay_scale, float key_eps) {
+  extern __shared__ float dp_smem[];     // [R] tanh of the lora hidden, then 32 floats of scratch
+  float* th = dp_smem;
+  float* scratch = dp_smem + R;
+  pdl_prologue();
+  const int t = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+  const int HD = H * D;
+  const long long row = (long long)t * (5 * HD + R);
+  for (int j = threadIdx.x; j < R; j += blockDim.x) th[j] = tanhf(source_load(proj, row + 5 * HD + j));
+  float k = 0.f, r = 0.f, v = 0.f, a = 0.f, w = 0.f;
+  const int ch = h * D + c;
+  if (c < D) {
+    r = source_load(proj, row + ch);
+    k = source_load(proj, row + HD + ch);
+    v = source_load(proj, row + 2 * HD + ch);
+    a = sigmoid_f32(__fadd_rn(source_load(proj, row + 4 * HD + ch), a_bias != nullptr ? a_bias[ch] : 0.f));
+  }
+  const float ss = block_sum(k * k, scratch);      // (also orders the writes of th before their reads)
+  if (c < D) {
+    float z = 0.f;
+    for (int j = 0; j < R; ++j) z = __fmaf_rn(load_as(w2, w_dtype, (long long)ch * R + j), th[j], z);
+    z = __fadd_rn(z, w0[ch]);
+    w = expf(-decay_scale * sigmoid_f32(z));
+    const float u = k / sqrtf(ss + key_eps);
+    float* out = packed + ((long long)t * H + h) * 6 * D + c;
+    out[0] = w;
+    out[D] = a * u;
+    out[2 * D] = u;
+    out[3 * D] = k;
+    out[4 * D] = r;
+    out[5 * D] = v;
+  }
+}
+
+// One block per (sequence, head, 32 value columns); a column's D state rows are spread over
+// 4 lanes (row i = 16 q + 4 s + e for lane s), each lane keeping its rows in registers over
+// all tokens of the sequence in this step.  The two sums over the rows (u . S and r . S) are
+// added in ascending order inside a lane and then over the 4 lanes by a butterfly: an order
+// that depends on D alone.  The token's six vectors are staged in shared memory two tokens
+// deep by asynchronous copies.
+template <int MAXR>
+__global__ void __launch_bounds__(128)
+delta_recurrence_kernel(const float* packed, float* state, float* o_out, const int* cu_q_lens,
+                        const int* state_slots, int H, int D) {
+  extern __shared__ float dr_smem[];           // [2][6][Dp]
+  const int Dp = (D + 15) / 16 * 16;
+  const int NR = Dp / 4;                       // rows per lane (<= MAXR)
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int s = threadIdx.x & 3;
+  const int c = blockIdx.z * 32 + (threadIdx.x >> 2);
+  const bool active = c < D;
+  for (int i = threadIdx.x; i < 2 * 6 * Dp; i += blockDim.x) dr_smem[i] = 0.f;   // the padding stays 0
+  pdl_prologue();
+  const int t0 = cu_q_lens[b], t1 = cu_q_lens[b + 1];
+  if (t1 <= t0) return;
+  const long long slot = state_slots[b];
+  float* S = state + ((slot * H + h) * D) * (long long)D;
+  float st[MAXR];
+#pragma unroll
+  for (int ii = 0; ii < MAXR; ++ii) {
+    const int i = (ii >> 2) * 16 + s * 4 + (ii & 3);
+    st[ii] = (ii < NR && active && i < D) ? S[(long long)i * D + c] : 0.f;
+  }
+  __syncthreads();
+  auto prefetch = [&](int t, int buf) {
+    const float* src = packed + ((long long)t * H + h) * 6 * D;
+    float* dst = dr_smem + buf * 6 * Dp;
+    for (int i = threadIdx.x; i < 6 * D; i += blockDim.x) {
+      const int vsel = i / D, d = i - vsel * D;
+      __pipeline_memcpy_async(dst + vsel * Dp + d, src + i, 4);
+    }
+    __pipeline_commit();
+  };
+  prefetch(t0, 0);
+  for (int t = t0; t < t1; ++t) {
+    const int buf = (t - t0) & 1;
+    if (t + 1 < t1) {
+      prefetch(t + 1, buf ^ 1);
+      __pipeline_wait_prior(1);
+    } else {
+      __pipeline_wait_prior(0);
+    }
+    __syncthreads();
+    const float* vw = dr_smem + buf * 6 * Dp;
+    const float* vb = vw + Dp;
+    const float* vu = vb + Dp;
+    const float* vk = vu + Dp;
+    const float* vr = vk + Dp;
+    const float v = active ? vr[Dp + c] : 0.f;
+    float dot = 0.f;
+#pragma unroll
+    for (int q = 0; q < MAXR / 4; ++q) {
+      if (q * 4 < NR) {
+        const float4 u4 = *reinterpret_cast<const float4*>(vu + q * 16 + s * 4);
+        dot = __fmaf_rn(u4.x, st[q * 4 + 0], dot);
+        dot = __fmaf_rn(u4.y, st[q * 4 + 1], dot);
+        dot = __fmaf_rn(u4.z, st[q * 4 + 2], dot);
+        dot = __fmaf_rn(u4.w, st[q * 4 + 3], dot);
+      }
+    }
+    dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, 1));
+    dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, 2));
+    float o = 0.f;
+#pragma unroll
+    for (int q = 0; q < MAXR / 4; ++q) {
+      if (q * 4 < NR) {
+        const int at = q * 16 + s * 4;
+        const float4 w4 = *reinterpret_cast<const float4*>(vw + at);
+        const float4 b4 = *reinterpret_cast<const float4*>(vb + at);
+        const float4 k4 = *reinterpret_cast<const float4*>(vk + at);
+        const float4 r4 = *reinterpret_cast<const float4*>(vr + at);
+        float n0 = __fmaf_rn(k4.x, v, __fmaf_rn(-b4.x, dot, __fmul_rn(w4.x, st[q * 4 + 0])));
+        float n1 = __fmaf_rn(k4.y, v, __fmaf_rn(-b4.y, dot, __fmul_rn(w4.y, st[q * 4 + 1])));
+        float n2 = __fmaf_rn(k4.z, v, __fmaf_rn(-b4.z, dot, __fmul_rn(w4.z, st[q * 4 + 2])));
+        float n3 = __fmaf_rn(k4.w, v, __fmaf_rn(-b4.w, dot, __fmul_rn(w4.w, st[q * 4 + 3])));
+        st[q * 4 + 0] = n0; st[q * 4 + 1] = n1; st[q * 4 + 2] = n2; st[q * 4 + 3] = n3;
+        o = __fmaf_rn(r4.x, n0, o);
+        o = __fmaf_rn(r4.y, n1, o);
+        o = __fmaf_rn(r4.z, n2, o);
+        o = __fmaf_rn(r4.w, n3, o);
+      }
+    }
+    o = __fadd_rn(o, __shfl_xor_sync(0xffffffffu, o, 1));
+    o = __fadd_rn(o, __shfl_xor_sync(0xffffffffu, o, 2));
+    if (active && s == 0) o_out[((long long)t * H + h) * D + c] = o;
+    __syncthreads();     // the next round's copies overwrite the other buffer, read one round ago
+  }
+#pragma unroll
+  for (int ii = 0; ii < MAXR; ++ii) {
+    const int i = (ii >> 2) * 16 + s * 4 + (ii & 3);
+    if (ii < NR && active && i < D) S[(long long)i * D + c] = st[ii];
+  }
+}
+
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * norm_w[h, :] * sigmoid(g[t, h, :])
+__global__ void delta_output_kernel(const float* o, Source proj, const float* norm_w, void* out, int out_dtype,
+                                    int H, int D, int R, float eps) {
+  __shared__ float scratch[32];
+  pdl_prologue();
+  const int t = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+  const int HD = H * D;
+  const long long at = ((long long)t * H + h) * D + c;
+  const float x = c < D ? o[at] : 0.f;
+  const float ss = block_sum(x * x, scratch);
+  if (c < D) {
+    const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+    const float g = source_load(proj, (long long)t * (5 * HD + R) + 3 * HD + h * D + c);
+    store_as(out, out_dtype, at, x * rstd * norm_w[h * D + c] * sigmoid_f32(g));
+  }
+}
+
+template <int MAXR>
+static int launch_recurrence(const float* packed, float* state, float* o_out, const int* cu_q_lens,
+                             const int* state_slots, int B, int H, int D, cudaStream_t st) {
+  const int Dp = (D + 15) / 16 * 16;
+  dib_launch(delta_recurrence_kernel<MAXR>, dim3(B, H, (D + 31) / 32), dim3(128),
+             sizeof(float) * 2 * 6 * Dp, st, packed, state, o_out, cu_q_lens, state_slots, H, D);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+extern "C" {
+
+int dib_delta_prepare(const void* proj, int kind, int splits, long long stride, const void* w2, int w_dtype,
+                      const float* w0, const float* a_bias, float* packed, int T_, int H, int D, int R,
+                      float decay_scale, float key_eps, cudaStream_t st) {
+  if (T_ == 0) return DIB_OK;
+  if (H < 1 || H > 65535 || D < 1 || D > 1024 || R < 0 || R > 8192) return DIB_BAD_SIZE;
+  if (w_dtype != 0 && w_dtype != 1) return DIB_BAD_DTYPE;
+  dib_launch(delta_prepare_kernel, dim3(T_, H), dim3((D + 31) / 32 * 32), sizeof(float) * (R + 32), st,
+             make_source(proj, kind, splits, stride), w2, w_dtype, w0, a_bias, packed, H, D, R, decay_scale,
+             key_eps);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// state [slots, H, D, D] float32; sequence b of the step owns tokens cu_q_lens[b] .. cu_q_lens[b+1]-1
+// and the state slot state_slots[b].
+int dib_delta_recurrence(const float* packed, float* state, float* o_out, const int* cu_q_lens,
+                         const int* state_slots, int B, int H, int D, cudaStream_t st) {
+  if (B == 0) return DIB_OK;
+  if (H < 1 || H > 65535 || D < 1 || D > 256) return DIB_BAD_SIZE;
+  if (D <= 64) return launch_recurrence<16>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+  if (D <= 128) return launch_recurrence<32>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+  return launch_recurrence<64>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+}
+
+int dib_delta_output(const float* o, const void* proj, int kind, int splits, long long stride,
+                     const float* norm_w, void* out, int out_dtype, int T_, int H, int D, int R, float eps,
+                     cudaStream_t st) {
+  if (T_ == 0) return DIB_OK;
+  if (H < 1 || H > 65535 || D < 1 || D > 1024) return DIB_BAD_SIZE;
+  if (out_dtype != 0 && out_dtype != 1) return DIB_BAD_DTYPE;
+  dib_launch(delta_output_kernel, dim3(T_, H), dim3((D + 31) / 32 * 32), 0, st, o,
+             make_source(proj, kind, splits, stride), norm_w, out, out_dtype, H, D, R, eps);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+}  // extern "C"

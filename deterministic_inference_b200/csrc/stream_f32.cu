@@ -1,0 +1,142 @@
+// Kernels of models whose residual stream is kept in float32 whatever the engine's
+// storage type is: token + learned position embedding, RMSNorm of the float32 stream
+// (alone, or after adding up to two scaled mixer outputs to it), the scaled sum as a
+// tensor, the xIELU activation and the soft cap of the logits.  All arithmetic is float32;
+// inputs that come from a matrix product may be its split-k partial products.
+#include "source.cuh"
+
+// out[t] = table[ids[t]] + pos_table[positions[t]], float32
+__global__ void embed_pos_kernel(const void* table, const void* pos_table, int dtype, const int* ids,
+                                 const int* positions, float* out, int T, int W, int V, int P) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  int id = ids[t], p = positions[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  p = p < 0 ? 0 : (p >= P ? P - 1 : p);
+  for (int c = threadIdx.x; c < W; c += blockDim.x)
+    out[(long long)t * W + c] =
+        __fadd_rn(load_as(table, dtype, (long long)id * W + c), load_as(pos_table, dtype, (long long)p * W + c));
+}
+
+// One block per row.  TERMS > 0: residual[row] += a0 * x0[row] (+ a1 * x1[row]) first, the
+// terms added in their order; then out[row] = residual[row] / sqrt(mean(residual[row]^2) + eps)
+// * w.  The sum of squares is taken by a block of a width that depends on W alone.
+template <int TERMS>
+__global__ void stream_norm_kernel(float* residual, Source x0, float a0, Source x1, float a1,
+                                   const float* w, void* out, int out_dtype, int W, float eps) {
+  __shared__ float scratch[32];
+  pdl_prologue();
+  const long long base = (long long)blockIdx.x * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float r = residual[base + c];
+    if (TERMS >= 1) r = __fmaf_rn(a0, source_load(x0, base + c), r);
+    if (TERMS >= 2) r = __fmaf_rn(a1, source_load(x1, base + c), r);
+    if (TERMS >= 1) residual[base + c] = r;
+    ss = __fmaf_rn(r, r, ss);
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = 1.0f / sqrtf(total / (float)W + eps);
+  if (out == nullptr) return;
+  for (int c = threadIdx.x; c < W; c += blockDim.x)
+    store_as(out, out_dtype, base + c, residual[base + c] * rstd * w[c]);
+}
+
+// out = a0 * x0 (+ a1 * x1), float32
+__global__ void weighted_sum_kernel(Source x0, float a0, Source x1, float a1, int terms, float* out,
+                                    long long n) {
+  pdl_prologue();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float r = __fmul_rn(a0, source_load(x0, i));
+    if (terms >= 2) r = __fmaf_rn(a1, source_load(x1, i), r);
+    out[i] = r;
+  }
+}
+
+// xIELU: z > 0: ap z^2 + z / 2;  z <= 0: an (exp(z) - 1 - z) + z / 2
+__global__ void xielu_kernel(Source z, float ap, float an, void* out, int out_dtype, long long n) {
+  pdl_prologue();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float x = source_load(z, i);
+    const float y = x > 0.f ? __fmaf_rn(__fmul_rn(ap, x), x, 0.5f * x)
+                            : __fmaf_rn(an, expm1f(x) - x, 0.5f * x);
+    store_as(out, out_dtype, i, y);
+  }
+}
+
+// x = cap * tanh(x / cap), in place
+__global__ void softcap_kernel(float* x, float cap, long long n) {
+  pdl_prologue();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+static inline int flat_grid(long long n, int block) {
+  long long g = (n + block - 1) / block;
+  return (int)(g > 148 * 16 ? 148 * 16 : (g < 1 ? 1 : g));
+}
+
+extern "C" {
+
+int dib_embed_pos(const void* table, const void* pos_table, int dtype, const int* ids,
+                  const int* positions, float* out, int T, int W, int V, int P, cudaStream_t st) {
+  if (T == 0) return DIB_OK;
+  if (dtype != 0 && dtype != 1) return DIB_BAD_DTYPE;
+  if (W < 1 || V < 1 || P < 1) return DIB_BAD_SIZE;
+  dib_launch(embed_pos_kernel, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, st, table, pos_table, dtype, ids,
+             positions, out, T, W, V, P);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// terms 0: norm of the stream alone.  x kinds: 0 float32 (splits >= 1), 1 bfloat16.
+// out may be null (terms > 0): the stream is updated and nothing is normed.
+int dib_stream_norm(float* residual, int terms, const void* x0, int kind0, int splits0, long long stride0,
+                    float a0, const void* x1, int kind1, int splits1, long long stride1, float a1,
+                    const float* w, void* out, int out_dtype, int rows, int W, float eps,
+                    cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (W < 1 || terms < 0 || terms > 2) return DIB_BAD_SIZE;
+  if (out != nullptr && out_dtype != 0 && out_dtype != 1) return DIB_BAD_DTYPE;
+  const Source s0 = make_source(x0, kind0, splits0, stride0), s1 = make_source(x1, kind1, splits1, stride1);
+  const dim3 grid(rows), block(W >= 2048 ? 512 : (W >= 512 ? 256 : 128));
+  if (terms == 0) dib_launch(stream_norm_kernel<0>, grid, block, 0, st, residual, s0, a0, s1, a1, w, out, out_dtype, W, eps);
+  else if (terms == 1) dib_launch(stream_norm_kernel<1>, grid, block, 0, st, residual, s0, a0, s1, a1, w, out, out_dtype, W, eps);
+  else dib_launch(stream_norm_kernel<2>, grid, block, 0, st, residual, s0, a0, s1, a1, w, out, out_dtype, W, eps);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_weighted_sum(int terms, const void* x0, int kind0, int splits0, long long stride0, float a0,
+                     const void* x1, int kind1, int splits1, long long stride1, float a1, float* out,
+                     long long n, cudaStream_t st) {
+  if (n == 0) return DIB_OK;
+  if (terms < 1 || terms > 2) return DIB_BAD_SIZE;
+  dib_launch(weighted_sum_kernel, dim3(flat_grid(n, 256)), dim3(256), 0, st,
+             make_source(x0, kind0, splits0, stride0), a0, make_source(x1, kind1, splits1, stride1), a1, terms,
+             out, n);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_xielu(const void* z, int kind, int splits, long long stride, float ap, float an, void* out,
+              int out_dtype, long long n, cudaStream_t st) {
+  if (n == 0) return DIB_OK;
+  if (out_dtype != 0 && out_dtype != 1) return DIB_BAD_DTYPE;
+  dib_launch(xielu_kernel, dim3(flat_grid(n, 256)), dim3(256), 0, st, make_source(z, kind, splits, stride), ap,
+             an, out, out_dtype, n);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_softcap(float* x, float cap, long long n, cudaStream_t st) {
+  if (n == 0) return DIB_OK;
+  dib_launch(softcap_kernel, dim3(flat_grid(n, 256)), dim3(256), 0, st, x, cap, n);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+}  // extern "C"

@@ -310,10 +310,13 @@ def check_packed(host: np.ndarray, lay: PackedLayout, cache, group_list: list, v
             if slots[bi] == 0:
                 continue        # a padding sequence: it lives on page 0 and slot 0 on purpose
             first_needed = 0
+            need_pages = -(-int(lens[bi]) // g.page_size)
+            row = bt[bi, :0]
             if g.window is not None:
                 first_needed = max(0, int(lens[bi]) - int(cu[bi + 1] - cu[bi]) - g.window + 1) // g.page_size
-            need_pages = -(-int(lens[bi]) // g.page_size)
-            row = bt[bi, first_needed:min(need_pages, lay.width)]
+                # the pages of the positions a window keeps readable for good
+                row = bt[bi, :min(-(-g.keep_first // g.page_size), first_needed, need_pages, lay.width)]
+            row = np.concatenate([row, bt[bi, first_needed:min(need_pages, lay.width)]])
             need(need_pages <= lay.width and bool((row > 0).all()),
                  f"group {g.key}: sequence {bi} has keys on a page it does not hold")
 

@@ -39,6 +39,9 @@ SOURCES = {
     "gemm_bf16_large": "gemm_bf16_large.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
+    "stream_f32": "stream_f32.cu",
+    "sigmoid_attention": "sigmoid_attention.cu",
+    "delta_rule": "delta_rule.cu",
 }
 HEADERS = ("common.cuh", "attention_merge.cuh")
 # further headers a library includes
@@ -46,6 +49,9 @@ EXTRA_HEADERS = {
     "attention_bf16": ("attention_bf16_kernels.cuh",),
     "decode_attention_noalloc": ("attention_bf16_kernels.cuh", "decode_attention_noalloc.h"),
     "attention_prefill_tc": ("attention_bf16_kernels.cuh",),
+    "stream_f32": ("source.cuh",),
+    "sigmoid_attention": ("source.cuh",),
+    "delta_rule": ("source.cuh",),
 }
 
 NVCC_FLAGS = [

@@ -258,7 +258,60 @@ class SplitAttention:
         return out.view(self.num_seqs, self.num_heads * self.head_dim)
 
 
-_DEFERRED = (SplitSum, GatedSplit, SplitAttention)
+class WeightedSum:
+    """sum_i scale_i * term_i that is not computed yet: the outputs of mixers that run side
+    by side, each a tensor or a ``SplitSum``.  The norm of a float32 residual stream adds
+    the terms to the stream in their order while it loads them; ``tensor()`` gives the sum
+    as a float32 tensor."""
+
+    def __init__(self, terms: list):
+        if not 1 <= len(terms) <= 2:
+            raise KernelError(f"a weighted sum of {len(terms)} terms has no kernel (1 or 2)")
+        self.terms = [(float(a), x) for a, x in terms]
+        self.dtype = torch.float32
+
+    @property
+    def shape(self):
+        return self.terms[0][1].shape
+
+    @property
+    def device(self):
+        return self.terms[0][1].device
+
+    def tensor(self) -> torch.Tensor:
+        rows, width = self.shape
+        out = torch.empty(rows, width, dtype=torch.float32, device=self.device)
+        st = _lib("stream_f32").dib_weighted_sum(c_int(len(self.terms)), *_terms_args(self.terms, 2),
+                                                 _ptr(out), c_longlong(rows * width), _stream())
+        _check(st, "weighted_sum")
+        return out
+
+
+_DEFERRED = (SplitSum, GatedSplit, SplitAttention, WeightedSum)
+
+
+def _source_args(x):
+    """(pointer, kind, splits, stride) of a kernel input that is a float32 or bfloat16
+    tensor or the split-k partial products of a matrix product."""
+    if isinstance(x, SplitSum):
+        s, m, n = x.parts.shape
+        return (_ptr(x.parts), c_int(0), c_int(s), c_longlong(m * n))
+    if isinstance(x, _DEFERRED):
+        x = x.tensor()
+    _need(x, "x")
+    return (_ptr(x), c_int(_dt(x, "x")), c_int(1), c_longlong(0))
+
+
+def _terms_args(terms: list, n: int) -> list:
+    """Arguments of ``n`` (source, scale) pairs; missing ones are null."""
+    out = []
+    for i in range(n):
+        if i < len(terms):
+            a, x = terms[i]
+            out += [*_source_args(x), c_float(a)]
+        else:
+            out += [c_void_p(0), c_int(0), c_int(1), c_longlong(0), c_float(0.0)]
+    return out
 
 
 def as_tensor(x):
@@ -655,3 +708,175 @@ def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch
                                _ptr(keep), _ptr(out), c_int(r), c_int(v), _stream())
     _check(st, "gumbel_sample")
     return out
+
+
+# ---------------------------------------------------------------- float32 residual stream
+
+def embedding_positions(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor,
+                        pos_table: torch.Tensor) -> torch.Tensor:
+    """float32 [T, W]: table[ids[t]] + pos_table[positions[t]]."""
+    _need(ids, "ids", torch.int32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    _need(table, "table", None, 2)
+    _need(pos_table, "pos_table", table.dtype, 2)
+    if table.shape[1] != pos_table.shape[1] or positions.shape[0] < ids.shape[0]:
+        raise KernelError(f"embedding_positions: table {tuple(table.shape)}, positions table "
+                          f"{tuple(pos_table.shape)}, {ids.shape[0]} ids, {positions.shape[0]} positions")
+    out = torch.empty(ids.shape[0], table.shape[1], dtype=torch.float32, device=table.device)
+    st = _lib("stream_f32").dib_embed_pos(_ptr(table), _ptr(pos_table), c_int(_dt(table, "table")), _ptr(ids),
+                                          _ptr(positions), _ptr(out), c_int(ids.shape[0]),
+                                          c_int(table.shape[1]), c_int(table.shape[0]),
+                                          c_int(pos_table.shape[0]), _stream())
+    _check(st, "embedding_positions")
+    return out
+
+
+def stream_rms_norm(stream: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype,
+                    add=None) -> torch.Tensor:
+    """RMSNorm of the float32 residual stream [rows, W], written in ``out_dtype``; with ``add``
+    (a tensor, a ``SplitSum`` or a ``WeightedSum``) the stream first takes stream += add in
+    place, in float32, and the norm is that of the sum."""
+    _need(stream, "stream", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    rows, w = stream.shape
+    if weight.shape[0] != w:
+        raise KernelError(f"stream_rms_norm: weight has {weight.shape[0]} elements, rows have {w}")
+    terms = []
+    if add is not None:
+        terms = add.terms if isinstance(add, WeightedSum) else [(1.0, add)]
+        for _, x in terms:
+            if tuple(x.shape) != (rows, w):
+                raise KernelError(f"stream_rms_norm: a term of shape {tuple(x.shape)} for a stream {(rows, w)}")
+    out = torch.empty(rows, w, dtype=out_dtype, device=stream.device)
+    st = _lib("stream_f32").dib_stream_norm(_ptr(stream), c_int(len(terms)), *_terms_args(terms, 2),
+                                            _ptr(weight), _ptr(out), c_int(_DT[out_dtype]), c_int(rows),
+                                            c_int(w), c_float(eps), _stream())
+    _check(st, "stream_rms_norm", f"row width {w}")
+    return out
+
+
+def xielu(z, alpha_p: float, alpha_n: float, out_dtype) -> torch.Tensor:
+    """z > 0: alpha_p z^2 + z / 2;  z <= 0: alpha_n (exp(z) - 1 - z) + z / 2; float32 arithmetic."""
+    rows, w = z.shape
+    out = torch.empty(rows, w, dtype=out_dtype, device=z.device)
+    st = _lib("stream_f32").dib_xielu(*_source_args(z), c_float(alpha_p), c_float(alpha_n), _ptr(out),
+                                      c_int(_DT[out_dtype]), c_longlong(rows * w), _stream())
+    _check(st, "xielu")
+    return out
+
+
+def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place: cap * tanh(logits / cap)."""
+    _need(logits, "logits", torch.float32)
+    st = _lib("stream_f32").dib_softcap(_ptr(logits), c_float(cap), c_longlong(logits.numel()), _stream())
+    _check(st, "softcap")
+    return logits
+
+
+# ---------------------------------------------------------------- attention without a softmax
+
+def qkv_bias_cache(qkv, bias, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
+                   kv_cache, slot_mapping, page_size: int, out_dtype) -> torch.Tensor:
+    """From the projection row [q heads | k heads | v heads] of each token plus ``bias`` (float32,
+    or None): q [T, Hq, D] is returned, k and v go to the token's slot of the paged cache (a page:
+    keys [Hkv, page_size, D], then values [Hkv, page_size, Dv]; slot = page * page_size + offset)."""
+    t, got = qkv.shape
+    width = num_heads * head_dim + num_kv_heads * (head_dim + v_head_dim)
+    if got != width:
+        raise KernelError(f"qkv has width {got}, expected {width}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != width:
+            raise KernelError(f"qkv bias has {bias.shape[0]} elements, expected {width}")
+    num_pages = 0
+    if kv_cache is not None:
+        _need(kv_cache, "kv_cache", out_dtype)
+        _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        page_elems = num_kv_heads * page_size * (head_dim + v_head_dim)
+        if kv_cache.numel() % page_elems or kv_cache.shape[0] != kv_cache.numel() // page_elems:
+            raise KernelError(f"kv_cache shape {tuple(kv_cache.shape)} is not [pages, ...] of pages of "
+                              f"{page_elems} elements")
+        num_pages = kv_cache.shape[0]
+    src = _source_args(qkv)
+    q = torch.empty(t, num_heads, head_dim, dtype=out_dtype, device=qkv.device)
+    st = _lib("sigmoid_attention").dib_qkv_bias_cache(
+        *src, _ptr(bias), _ptr(q), _ptr(kv_cache), _ptr(slot_mapping), c_int(t), c_int(num_heads),
+        c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim), c_int(page_size), c_longlong(num_pages),
+        c_int(_DT[out_dtype]), _stream())
+    _check(st, "qkv_bias_cache")
+    return q
+
+
+def sigmoid_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float, head_bias,
+                      v_head_dim: int, page_size: int, window=None, keep_first: int = 0) -> torch.Tensor:
+    """[T, Hq, Dv]: every token's sum over its visible cached keys j of
+    sigmoid(q . k_j * scale + head_bias[head]) * v_j (no normalisation over keys).  A query at
+    position p sees j <= p with p - j < window or j < keep_first (no window: every j <= p)."""
+    _need(q, "q", None, 3)
+    _need(kv_cache, "kv_cache", q.dtype)
+    t, hq, d = q.shape
+    page_elems = kv_cache.numel() // kv_cache.shape[0]
+    hkv, rem = divmod(page_elems, page_size * (d + v_head_dim))
+    if rem or hkv < 1 or hq % hkv:
+        raise KernelError(f"sigmoid_attention: q {tuple(q.shape)}, value size {v_head_dim}, pages of "
+                          f"{page_elems} elements at page size {page_size}")
+    if head_bias is not None:
+        _need(head_bias, "head_bias", torch.float32, 1)
+        if head_bias.shape[0] != hq:
+            raise KernelError(f"sigmoid_attention: {head_bias.shape[0]} head biases for {hq} heads")
+    _need(meta.block_table, "block_table", torch.int32, 2)
+    _need(meta.token_seq, "token_seq", torch.int32, 1)
+    _need(meta.positions, "positions", torch.int32, 1)
+    out = torch.empty(t, hq, v_head_dim, dtype=q.dtype, device=q.device)
+    st = _lib("sigmoid_attention").dib_sigmoid_attention(
+        _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
+        _ptr(meta.token_seq), _ptr(meta.positions), _ptr(head_bias), c_int(t), c_int(hq), c_int(hkv), c_int(d),
+        c_int(v_head_dim), c_int(page_size), c_float(scale), c_int(int(window) if window else 0),
+        c_int(int(keep_first)), c_int(_dt(q, "q")), _stream())
+    _check(st, "sigmoid_attention", f"heads {hq}/{hkv}, sizes {d}/{v_head_dim}")
+    return out
+
+
+# ---------------------------------------------------------------- generalised delta rule
+
+def delta_rule(proj, w2: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: torch.Tensor,
+               state: torch.Tensor, step, num_heads: int, head_dim: int, lora_rank: int,
+               decay_scale: float, key_eps: float, norm_eps: float, out_dtype) -> torch.Tensor:
+    """The recurrence S_t = diag(w) S_(t-1) - (a * u)(u^T S_(t-1)) + k v^T, o_t = S_t^T r per head,
+    over every sequence's tokens of the step, from and to ``state`` [slots, H, D, D] (float32,
+    rows ``step.state_slots``); then each head's o over its root mean square, times
+    ``norm_weight``, times sigmoid(g): [T, H * D] in ``out_dtype``.  ``proj`` rows are
+    [r | k | v | g | a | lora hidden]; w = exp(-decay_scale * sigmoid(w2 tanh(lora hidden) + w0)),
+    a = sigmoid(a + a_bias), u = k / sqrt(sum(k^2) + key_eps)."""
+    t, got = proj.shape
+    hd = num_heads * head_dim
+    if got != 5 * hd + lora_rank:
+        raise KernelError(f"delta_rule: projection rows of {got}, expected {5 * hd + lora_rank}")
+    _need(w2, "w2", None, 2)
+    _need(w0, "w0", torch.float32, 1)
+    _need(norm_weight, "norm_weight", torch.float32, 1)
+    _need(state, "state", torch.float32, 4)
+    if tuple(w2.shape) != (hd, lora_rank) or w0.shape[0] != hd or norm_weight.shape[0] != hd \
+            or tuple(state.shape[1:]) != (num_heads, head_dim, head_dim):
+        raise KernelError("delta_rule: a weight or the state does not fit the head count and size")
+    if a_bias is not None:
+        _need(a_bias, "a_bias", torch.float32, 1)
+    lib = _lib("delta_rule")
+    src = _source_args(proj)
+    dev = state.device
+    packed = torch.empty(t, num_heads, 6, head_dim, dtype=torch.float32, device=dev)
+    st = lib.dib_delta_prepare(*src, _ptr(w2), c_int(_dt(w2, "w2")), _ptr(w0), _ptr(a_bias), _ptr(packed),
+                               c_int(t), c_int(num_heads), c_int(head_dim), c_int(lora_rank),
+                               c_float(decay_scale), c_float(key_eps), _stream())
+    _check(st, "delta_rule(prepare)", f"heads {num_heads} of {head_dim}, rank {lora_rank}")
+    o = torch.empty(t, num_heads, head_dim, dtype=torch.float32, device=dev)
+    st = lib.dib_delta_recurrence(_ptr(packed), _ptr(state), _ptr(o), _ptr(step.cu_q_lens),
+                                  _ptr(step.state_slots), c_int(step.num_seqs), c_int(num_heads),
+                                  c_int(head_dim), _stream())
+    _check(st, "delta_rule(recurrence)", f"heads of {head_dim} (at most 256)")
+    out = torch.empty(t, hd, dtype=out_dtype, device=dev)
+    st = lib.dib_delta_output(_ptr(o), *src, _ptr(norm_weight), _ptr(out), c_int(_DT[out_dtype]), c_int(t),
+                              c_int(num_heads), c_int(head_dim), c_int(lora_rank), c_float(norm_eps), _stream())
+    _check(st, "delta_rule(output)")
+    return out
+

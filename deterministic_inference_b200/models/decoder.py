@@ -93,7 +93,10 @@ class DecoderModel:
 
     def forward(self, step, cache_manager) -> torch.Tensor:
         """float32 logits [R, V] at ``step.logit_indices``."""
-        hidden = self.embedding.forward(step.input_ids)
+        if getattr(self.embedding, "needs_positions", False):
+            hidden = self.embedding.forward(step.input_ids, step.positions)
+        else:
+            hidden = self.embedding.forward(step.input_ids)
         residual = None
         for e in self.plan.schedule:
             cache = cache_manager.view(e.cache, step, writes=e.writes_cache)

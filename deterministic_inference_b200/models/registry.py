@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``architectures[0]`` of config.json)
+"""One registry from an architecture's name (``architectures[0]`` or ``architecture`` of config.json)
 to its configuration class.  The reference has none: it asserts
 ``model_type == "qwen3"`` and imports its model class (sid/model/loader.py:32,
 sid/engine/model_runner.py:23).
@@ -15,6 +15,7 @@ from pathlib import Path
 
 import torch
 
+from ..config.gamilorn_config import GamilornConfig
 from ..config.model_config import Qwen3Config
 from .decoder import DecoderModel
 
@@ -31,6 +32,7 @@ def register_architecture(name: str, config_class: type) -> None:
 
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
+register_architecture("Gamilorn", GamilornConfig)
 
 
 def config_from_dir(model_dir):
@@ -39,7 +41,8 @@ def config_from_dir(model_dir):
     if not path.exists():
         raise FileNotFoundError(f"{path} does not exist")
     raw = json.loads(path.read_text())
-    archs = raw.get("architectures") or []
+    # ``architectures`` (a list, the first entry counts) or ``architecture`` (one name)
+    archs = raw.get("architectures") or ([raw["architecture"]] if raw.get("architecture") else [])
     if not archs:
         raise UnknownArchitecture(f"{path} names no architecture; known: {sorted(MODEL_REGISTRY)}")
     if archs[0] not in MODEL_REGISTRY:

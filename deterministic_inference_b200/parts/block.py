@@ -27,3 +27,29 @@ class PreNormBlock(Block):
         hidden, residual = self.feed_forward_norm.add_forward(hidden, residual)
         hidden = self.feed_forward.forward(hidden)
         return hidden, residual
+
+
+@register_block("pre_norm_f32_stream")
+class PreNormStreamBlock(Block):
+    """The same arrangement with the residual stream in float32: x <- x + mixer(norm(x)), then
+    x <- x + feed_forward(norm(x)), every addition in float32 whatever type the parts
+    compute in.  The stream comes in as float32 (from the embedding, or as the stream and
+    the pending output of the layer before); a layer without a feed-forward (kind "none")
+    hands its mixer's output on as the pending term."""
+
+    def __init__(self, ctx, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def forward(self, hidden, residual, step, cache):
+        if residual is None:
+            residual = hidden
+            hidden = self.mixer_norm.forward(residual)
+        else:
+            hidden, residual = self.mixer_norm.add_forward(hidden, residual)
+        hidden = self.mixer.forward(hidden, step, cache)
+        if self.feed_forward.kind == "none":
+            return hidden, residual
+        hidden, residual = self.feed_forward_norm.add_forward(hidden, residual)
+        hidden = self.feed_forward.forward(hidden)
+        return hidden, residual

@@ -1,5 +1,5 @@
 """The two ends of the decoder as parts: the token embedding (a row gather,
-sid/model/qwen3.py:93) and the head on the wanted rows (a matrix product whose float32
+sid/model/qwen3.py:93; or a row gather plus a learned position vector) and the head on the wanted rows (a matrix product whose float32
 accumulator is the logits, sid/model/qwen3.py:113-115).  The head has a weight of its own
 or shares the embedding's table (sid/model/loader.py:74-82)."""
 
@@ -34,12 +34,44 @@ class GatherEmbedding(TokenEmbedding):
         return ops.embedding(ids, self.weight)
 
 
+@register_embedding("token_position_embedding")
+class TokenPositionEmbedding(TokenEmbedding):
+    """x = table[token] + positions[p]: a learned vector per position (counted from 0 in each
+    sequence) is added, unscaled, to the token's row.  The sum is float32: this embedding
+    opens a residual stream that is kept in float32."""
+
+    needs_positions = True
+
+    def __init__(self, ctx, name: str, position_name: str, vocab_size: int, hidden_size: int,
+                 max_positions: int):
+        self.name, self.position_name = name, position_name
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.max_positions = int(max_positions)
+        self.weight = self.positions = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.vocab_size, self.hidden_size), role="table"),
+                TensorSpec(self.position_name, (self.max_positions, self.hidden_size), role="table")]
+
+    def load(self, tensors):
+        self.weight, self.positions = tensors[self.name], tensors[self.position_name]
+
+    def table(self):
+        return self.weight
+
+    def forward(self, ids, positions=None):
+        return ops.embedding_positions(ids, positions, self.weight, self.positions)
+
+
 @register_head("linear_head")
 class LinearHead(Head):
     """logits = rows @ W^T in float32.  ``name`` None: W is the embedding's table."""
 
-    def __init__(self, ctx, name: Optional[str], vocab_size: int, hidden_size: int):
+    def __init__(self, ctx, name: Optional[str], vocab_size: int, hidden_size: int,
+                 softcap: Optional[float] = None):
         self.name, self.vocab_size, self.hidden_size = name, int(vocab_size), int(hidden_size)
+        # softcap c: logits <- c * tanh(logits / c)
+        self.softcap = None if softcap is None else float(softcap)
         self.tied = name is None
         self.weight = None
 
@@ -53,4 +85,5 @@ class LinearHead(Head):
 
     def forward(self, rows):
         # logits leave as a plain tensor (the product may come as split-k partials)
-        return ops.as_tensor(ops.linear(rows, self.weight, out_dtype=torch.float32))
+        logits = ops.as_tensor(ops.linear(rows, self.weight, out_dtype=torch.float32))
+        return logits if self.softcap is None else ops.softcap_(logits, self.softcap)

@@ -108,9 +108,18 @@ class PagedKVSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None   # size of a value head; None: that of a key head
+    keep_first: int = 0                # with a window: the first ``keep_first`` keys stay readable
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
     def group_key(self) -> tuple:
-        return ("paged_kv", self.num_kv_heads, self.head_dim, self.window)
+        key = ("paged_kv", self.num_kv_heads, self.head_dim, self.window)
+        if self.value_dim != self.head_dim or (self.window is not None and self.keep_first):
+            key += (self.value_dim, self.keep_first if self.window is not None else 0)
+        return key
 
 
 @dataclass(frozen=True)
@@ -122,3 +131,31 @@ class StateSpec:
 
     def group_key(self) -> tuple:
         return ("state", tuple(self.shape), self.dtype)
+
+
+@dataclass(frozen=True)
+class CompositeSpec:
+    """Cache need of a mixer made of several mixers that run side by side on the same
+    input: one member per inner mixer (``None`` for one that keeps nothing).  The cache
+    manager keeps every member in the group of its own kind; the mixer sees them as
+    ``CacheView.members``, in this order."""
+
+    members: tuple
+
+    def group_key(self) -> tuple:
+        return ("composite",) + tuple(None if m is None else m.group_key() for m in self.members)
+
+
+def flatten_cache_specs(cache_specs: dict) -> dict:
+    """cache id -> need, with every ``CompositeSpec`` replaced by its members under the ids
+    ``(cache id, member index)``; members that keep nothing are left out."""
+    flat = {}
+    for cid in sorted(cache_specs):
+        spec = cache_specs[cid]
+        if isinstance(spec, CompositeSpec):
+            for mi, m in enumerate(spec.members):
+                if m is not None:
+                    flat[(cid, mi)] = m
+        else:
+            flat[cid] = spec
+    return flat

@@ -129,13 +129,15 @@ def gated_linear(x, w_gate_up):
 
 def gather_rows(x, index):
     """sid/model/qwen3.py:113"""
+    if hasattr(x, "terms"):
+        x = _plain(x)
     return x[index.long()].contiguous()
 
 
 def linear(x, weight, out_dtype=None):
     """sid/model/qwen3.py:38 (float32 accumulation)."""
     y = x.float() @ weight.float().T
-    return y.to(out_dtype or x.dtype)
+    return y.to(out_dtype or x.dtype)     # (x is a norm's output or a kernel's: a tensor)
 
 
 def argmax(logits):
@@ -189,5 +191,114 @@ def gumbel_sample(logits, temperatures, seeds, sample_positions, keep=None, top_
     return torch.where(temperatures > 0, sampled, greedy).to(torch.int32)
 
 
-ALL = ("patch_token_ids", "embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
+# ---- kernels of models with a float32 residual stream, attention without a softmax and a
+# ---- delta-rule recurrence (each from its equations; signatures of ``ops``)
+
+def _plain(x):
+    """A float32 tensor of a weighted sum that is not added up yet, or of a tensor."""
+    if hasattr(x, "terms"):
+        total = None
+        for a, t in x.terms:
+            total = a * _plain(t) if total is None else total + a * _plain(t)
+        return total
+    return x.float()
+
+
+def embedding_positions(ids, positions, table, pos_table):
+    return table[ids.long()].float() + pos_table[positions[:ids.shape[0]].long()].float()
+
+
+def stream_rms_norm(stream, weight, eps, out_dtype, add=None):
+    if add is not None:
+        stream += _plain(add)
+    return _rms(stream, weight, eps).to(out_dtype)
+
+
+def xielu(z, alpha_p, alpha_n, out_dtype):
+    z = _plain(z)
+    pos = alpha_p * z * z + 0.5 * z
+    neg = alpha_n * (torch.expm1(torch.clamp(z, max=0.0)) - z) + 0.5 * z
+    return torch.where(z > 0, pos, neg).to(out_dtype)
+
+
+def softcap_(logits, cap):
+    logits.copy_(cap * torch.tanh(logits / cap))
+    return logits
+
+
+def qkv_bias_cache(qkv, bias, num_heads, num_kv_heads, head_dim, v_head_dim, kv_cache, slot_mapping,
+                   page_size, out_dtype):
+    x = _plain(qkv)
+    if bias is not None:
+        x = x + bias
+    t = x.shape[0]
+    nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+    if kv_cache is not None:
+        flat = kv_cache.view(kv_cache.shape[0], -1)
+        k = x[:, nq:nq + nk].view(t, num_kv_heads, head_dim).to(out_dtype)
+        v = x[:, nq + nk:].view(t, num_kv_heads, v_head_dim).to(out_dtype)
+        v_base = num_kv_heads * page_size * head_dim
+        for i, slot in enumerate(slot_mapping.tolist()[:t]):
+            if slot < 0:
+                continue
+            page, off = divmod(slot, page_size)
+            for g in range(num_kv_heads):
+                a = (g * page_size + off) * head_dim
+                flat[page, a:a + head_dim] = k[i, g]
+                a = v_base + (g * page_size + off) * v_head_dim
+                flat[page, a:a + v_head_dim] = v[i, g]
+    return x[:, :nq].reshape(t, num_heads, head_dim).to(out_dtype)
+
+
+def sigmoid_attention(q, kv_cache, meta, scale, head_bias, v_head_dim, page_size, window=None, keep_first=0):
+    t, hq, d = q.shape
+    flat = kv_cache.view(kv_cache.shape[0], -1)
+    hkv = flat.shape[1] // (page_size * (d + v_head_dim))
+    keys_of = flat[:, :hkv * page_size * d].view(-1, hkv, page_size, d)
+    values_of = flat[:, hkv * page_size * d:].view(-1, hkv, page_size, v_head_dim)
+    out = torch.zeros(t, hq, v_head_dim, dtype=torch.float32)
+    seqs, positions = meta.token_seq.tolist(), meta.positions.tolist()
+    for i in range(t):
+        p = positions[i]
+        js = [j for j in range(p + 1) if not window or p - j < window or j < keep_first]
+        idx = torch.tensor(js)
+        pages = meta.block_table[seqs[i], idx // page_size].long()
+        k = keys_of[pages, :, idx % page_size].float()        # [n, Hkv, D]
+        v = values_of[pages, :, idx % page_size].float()
+        for h in range(hq):
+            g = h // (hq // hkv)
+            sc = (k[:, g] @ q[i, h].float()) * scale
+            if head_bias is not None:
+                sc = sc + head_bias[h]
+            out[i, h] = torch.sigmoid(sc) @ v[:, g]
+    return out.to(q.dtype)
+
+
+def delta_rule(proj, w2, w0, a_bias, norm_weight, state, step, num_heads, head_dim, lora_rank,
+               decay_scale, key_eps, norm_eps, out_dtype):
+    x = _plain(proj)
+    t, hd = x.shape[0], num_heads * head_dim
+    shape = (t, num_heads, head_dim)
+    r, k, v, g = (x[:, i * hd:(i + 1) * hd].reshape(shape) for i in range(4))
+    a = x[:, 4 * hd:5 * hd]
+    if a_bias is not None:
+        a = a + a_bias
+    a = torch.sigmoid(a).reshape(shape)
+    w = torch.exp(-decay_scale * torch.sigmoid(torch.tanh(x[:, 5 * hd:]) @ w2.float().T + w0)).reshape(shape)
+    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + key_eps)
+    o = torch.zeros(shape)
+    cu, slots = step.cu_q_lens.tolist(), step.state_slots.tolist()
+    for b in range(len(slots)):
+        s = state[slots[b]]
+        for i in range(cu[b], cu[b + 1]):
+            us = torch.einsum("hk,hkv->hv", u[i], s)
+            s = w[i][:, :, None] * s - (a[i] * u[i])[:, :, None] * us[:, None, :] + k[i][:, :, None] * v[i][:, None, :]
+            o[i] = torch.einsum("hkv,hk->hv", s, r[i])
+        state[slots[b]] = s
+    o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + norm_eps)
+    return (o.reshape(t, hd) * norm_weight * torch.sigmoid(g.reshape(t, hd))).to(out_dtype)
+
+
+ALL = ("embedding_positions", "stream_rms_norm", "xielu", "softcap_", "qkv_bias_cache", "sigmoid_attention",
+       "delta_rule", "patch_token_ids", "embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
        "paged_attention", "silu_mul", "gated_linear", "gather_rows", "linear", "argmax", "gumbel_sample")
