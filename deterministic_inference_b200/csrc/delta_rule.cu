@@ -68,12 +68,13 @@ delta_recurrence_kernel(const float* packed, float* state, float* o_out, const i
   const int t0 = cu_q_lens[b], t1 = cu_q_lens[b + 1];
   if (t1 <= t0) return;
   const long long slot = state_slots[b];
+  const bool kept = slot != 0;       // slot 0 belongs to padding sequences: zero state, nothing stored
   float* S = state + ((slot * H + h) * D) * (long long)D;
   float st[MAXR];
 #pragma unroll
   for (int ii = 0; ii < MAXR; ++ii) {
     const int i = (ii >> 2) * 16 + s * 4 + (ii & 3);
-    st[ii] = (ii < NR && active && i < D) ? S[(long long)i * D + c] : 0.f;
+    st[ii] = (kept && ii < NR && active && i < D) ? S[(long long)i * D + c] : 0.f;
   }
   __syncthreads();
   auto prefetch = [&](int t, int buf) {
@@ -142,7 +143,7 @@ delta_recurrence_kernel(const float* packed, float* state, float* o_out, const i
 #pragma unroll
   for (int ii = 0; ii < MAXR; ++ii) {
     const int i = (ii >> 2) * 16 + s * 4 + (ii & 3);
-    if (ii < NR && active && i < D) S[(long long)i * D + c] = st[ii];
+    if (kept && ii < NR && active && i < D) S[(long long)i * D + c] = st[ii];
   }
 }
 
@@ -189,7 +190,8 @@ int dib_delta_prepare(const void* proj, int kind, int splits, long long stride, 
 }
 
 // state [slots, H, D, D] float32; sequence b of the step owns tokens cu_q_lens[b] .. cu_q_lens[b+1]-1
-// and the state slot state_slots[b].
+// and the state slot state_slots[b].  Slot 0 is no request's: a sequence on it starts from a
+// zero state and leaves none.
 int dib_delta_recurrence(const float* packed, float* state, float* o_out, const int* cu_q_lens,
                          const int* state_slots, int B, int H, int D, cudaStream_t st) {
   if (B == 0) return DIB_OK;

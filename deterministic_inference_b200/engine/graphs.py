@@ -81,6 +81,9 @@ class DecodeGraphs:
         self.min_width = min_width
         self.graphs: dict[tuple, _Captured] = {}
         self.group_list = list(self.cache.page_groups.values())
+        # per-request state is no obstacle when every mixer that keeps some finds its slots
+        # on the device (``state_on_device``) and leaves state slot 0 alone
+        self.state_capturable = not self.cache.state_groups or model.state_on_device()
         self.replays = 0
         self.captures = 0
         self.capture_seconds = 0.0
@@ -92,10 +95,9 @@ class DecodeGraphs:
         self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
 
     def usable(self, entries) -> bool:
-        """Pure-decode steps only; and not while a part keeps per-request state: the
-        capture runs the model twice as a warm-up, which would advance that state, and
-        such a part may read its slots on the host."""
-        return (not self.cache.state_groups and 0 < len(entries) <= self.max_batch
+        """Pure-decode steps only; and not while a part keeps per-request state that it
+        reads through the host (its slots would be frozen into the graph)."""
+        return (self.state_capturable and 0 < len(entries) <= self.max_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
     # ---- capture ---------------------------------------------------------------
@@ -123,7 +125,14 @@ class DecodeGraphs:
         upper = w * self.cache.page_size
         batch = step_views(static, lay, self.group_list, [1] * bb, [upper] * bb, [0] * bb, bb,
                            [[i] for i in range(bb)], list(range(bb)))
-        fill_packed(host.numpy(), lay, shape, self.cache, self.group_list)
+        if self.cache.state_groups:
+            # the warm-up runs would advance the requests' state: they run on padding
+            # sequences alone (page 0, state slot 0), the step's own metadata comes with
+            # the first replay
+            warm = describe_step([SequenceInput(0, [0], 0, [0])] * bb, self.cache)
+            fill_packed(host.numpy(), lay, warm, self.cache, self.group_list)
+        else:
+            fill_packed(host.numpy(), lay, shape, self.cache, self.group_list)
         static.copy_(host, non_blocking=True)
         # warm up on a side stream (library handles, lazy module loading), then capture
         side = torch.cuda.Stream(device=dev)

@@ -89,6 +89,20 @@ class DecoderModel:
                                      f"{spec} vs {out[e.cache]}")
         return out
 
+    def state_on_device(self) -> bool:
+        """Whether every mixer that keeps per-request state finds its slots through the
+        step's device metadata alone (``state_on_device``) and neither reads nor writes state
+        slot 0: a step of such a model can be captured as a CUDA graph and replayed for
+        other requests."""
+        from ..parts.spec import CompositeSpec, StateSpec
+
+        def keeps_state(spec):
+            if isinstance(spec, CompositeSpec):
+                return any(keeps_state(m) for m in spec.members)
+            return isinstance(spec, StateSpec)
+
+        return all(getattr(m, "state_on_device", False) for m in self.mixers if keeps_state(m.cache_spec()))
+
     # ---- one step ---------------------------------------------------------------
 
     def forward(self, step, cache_manager) -> torch.Tensor:

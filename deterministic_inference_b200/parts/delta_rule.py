@@ -27,6 +27,10 @@ from .spec import StateSpec, TensorSpec
 
 @register_mixer("delta_rule")
 class DeltaRule(Mixer):
+    # the kernels take the sequences' state slots from the step's device metadata, and a
+    # sequence on state slot 0 (padding) starts from zero and stores nothing
+    state_on_device = True
+
     def __init__(self, ctx, prefix: str, hidden_size: int, num_heads: int, head_dim: int, decay_rank: int,
                  norm_eps: float, decay_scale: float = math.exp(-0.5), key_eps: float = 1e-6,
                  names: Optional[dict] = None):

@@ -8,7 +8,7 @@ from __future__ import annotations
 from ..kernels import ops
 from .base import Mixer
 from .registry import MIXERS, register_mixer
-from .spec import CompositeSpec
+from .spec import CompositeSpec, StateSpec
 
 
 @register_mixer("parallel")
@@ -18,6 +18,11 @@ class ParallelMixers(Mixer):
             raise ValueError(f"parallel mixers: {len(branches)} branches and {len(scales)} scales")
         self.branches = [MIXERS.build(spec, ctx) for spec in branches]
         self.scales = [float(s) for s in scales]
+
+    @property
+    def state_on_device(self) -> bool:
+        return all(getattr(b, "state_on_device", False) or not isinstance(b.cache_spec(), StateSpec)
+                   for b in self.branches)
 
     def tensor_specs(self):
         return [s for b in self.branches for s in b.tensor_specs()]

@@ -100,17 +100,26 @@ def softcap(x, c):
 
 # ---- the model ---------------------------------------------------------------------------------
 
-def left_branch(h, w, p, c):
+def _keep(x):
+    return x
+
+
+def as_stored_bf16(x):
+    """What a tensor is after a trip through bfloat16 storage."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def left_branch(h, w, p, c, rnd=_keep):
     n = h.shape[0]
-    q = (h @ w[p + "q"].T + w[p + "q.b"]).view(n, c["heads"], c["dim"])
-    k = (h @ w[p + "k"].T + w[p + "k.b"]).view(n, c["kv_heads"], c["dim"])
-    v = (h @ w[p + "v"].T + w[p + "v.b"]).view(n, c["kv_heads"], c["vdim"])
+    q = rnd(h @ w[p + "q"].T + w[p + "q.b"]).view(n, c["heads"], c["dim"])
+    k = rnd(h @ w[p + "k"].T + w[p + "k.b"]).view(n, c["kv_heads"], c["dim"])
+    v = rnd(h @ w[p + "v"].T + w[p + "v.b"]).view(n, c["kv_heads"], c["vdim"])
     o = sigmoid_window_attention(q, k, v, c["scale"], w[p + "pb"], c["mask"]["size"],
                                  c["mask"].get("keep_first", 0))
-    return o.reshape(n, -1) @ w[p + "o"].T
+    return rnd(rnd(o).reshape(n, -1) @ w[p + "o"].T)
 
 
-def right_branch(h, w, p, c, eps):
+def right_branch(h, w, p, c, eps, rnd=_keep):
     n = h.shape[0]
     shape = (n, c["heads"], c["dim"])
     r, k, v = ((h @ w[p + x].T).view(shape) for x in ("r", "k", "v"))
@@ -118,12 +127,16 @@ def right_branch(h, w, p, c, eps):
     rate = torch.sigmoid(h @ w[p + "a"].T + w[p + "a.b"]).view(shape)
     o, _ = delta_rule(r, k, v, decay, rate)
     o = unit_rms(o, eps).reshape(n, -1) * w[p + "norm"] * torch.sigmoid(h @ w[p + "g"].T)
-    return o @ w[p + "o"].T
+    return rnd(rnd(o) @ w[p + "o"].T)
 
 
-def forward(cfg, w, tokens, streams=None):
+def forward(cfg, w, tokens, streams=None, store_bf16=False):
     """Logits [n, vocab] of one whole sequence; ``streams``: a list that receives the residual
-    stream after every layer."""
+    stream after every layer.  ``store_bf16``: what an engine that keeps its activations in
+    bfloat16 between kernels would round is rounded (norm outputs, q/k/v, the mixers' and the
+    feed-forward's inner results and outputs), everything else stays as it is: a yardstick
+    for what storage rounding alone does to the logits."""
+    rnd = as_stored_bf16 if store_bf16 else _keep
     tokens = torch.as_tensor(tokens)
     n = tokens.shape[0]
     eps = cfg["norm"]["eps"]
@@ -131,16 +144,16 @@ def forward(cfg, w, tokens, streams=None):
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         m = layer["mixer"]
-        h = zero_centred_norm(x, w[p + "norm1"], eps)
-        x = x + m["left_scale"] * left_branch(h, w, p + "mix.left.", m["left"]) \
-            + m["right_scale"] * right_branch(h, w, p + "mix.right.", m["right"], eps)
+        h = rnd(zero_centred_norm(x, w[p + "norm1"], eps))
+        x = x + m["left_scale"] * left_branch(h, w, p + "mix.left.", m["left"], rnd) \
+            + m["right_scale"] * right_branch(h, w, p + "mix.right.", m["right"], eps, rnd)
         if layer.get("mlp") is not None:
-            h = zero_centred_norm(x, w[p + "norm2"], eps)
+            h = rnd(zero_centred_norm(x, w[p + "norm2"], eps))
             act = w[p + "mlp.act"]
-            x = x + xielu(h @ w[p + "mlp.up"].T, act[0], act[1]) @ w[p + "mlp.down"].T
+            x = x + rnd(rnd(xielu(h @ w[p + "mlp.up"].T, act[0], act[1])) @ w[p + "mlp.down"].T)
         if streams is not None:
             streams.append(x.clone())
-    return softcap(zero_centred_norm(x, w["final.norm"], eps) @ w["head"].T, cfg["logit_softcap"])
+    return softcap(rnd(zero_centred_norm(x, w["final.norm"], eps)) @ w["head"].T, cfg["logit_softcap"])
 
 
 def generate(cfg, w, prompt, num_new):

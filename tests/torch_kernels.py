@@ -289,12 +289,14 @@ def delta_rule(proj, w2, w0, a_bias, norm_weight, state, step, num_heads, head_d
     o = torch.zeros(shape)
     cu, slots = step.cu_q_lens.tolist(), step.state_slots.tolist()
     for b in range(len(slots)):
-        s = state[slots[b]]
+        # state slot 0 is no request's: a sequence on it starts from zero and leaves nothing
+        s = state[slots[b]] if slots[b] else torch.zeros_like(state[0])
         for i in range(cu[b], cu[b + 1]):
             us = torch.einsum("hk,hkv->hv", u[i], s)
             s = w[i][:, :, None] * s - (a[i] * u[i])[:, :, None] * us[:, None, :] + k[i][:, :, None] * v[i][:, None, :]
             o[i] = torch.einsum("hkv,hk->hv", s, r[i])
-        state[slots[b]] = s
+        if slots[b]:
+            state[slots[b]] = s
     o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + norm_eps)
     return (o.reshape(t, hd) * norm_weight * torch.sigmoid(g.reshape(t, hd))).to(out_dtype)
 
