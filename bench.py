@@ -279,6 +279,229 @@ def model_bytes_and_flops(cfg, layers: int, batch: int, ctx: float, prefill_toke
     return decode_bytes, prefill_flops
 
 
+# ---- another design beside the closest existing model, at equal layer sizes -------------------
+
+DESIGN_SIZES = {
+    # name -> (the Qwen3 preset of these layer sizes, the Gamilorn mixer sizes that go with them)
+    "0_6b": ("qwen3_0_6b", dict(window=1024, keep=4, r_heads=16, r_dim=64)),
+    "8b": ("qwen3_8b", dict(window=4096, keep=4, r_heads=64, r_dim=64)),
+}
+
+
+def gamilorn_like(q, layers: int, window: int, keep: int, r_heads: int, r_dim: int):
+    """A Gamilorn configuration with the layer sizes of the Qwen3 configuration ``q``."""
+    from deterministic_inference_b200.config.gamilorn_config import GamilornConfig
+    layer = {"type": "parallel",
+             "mixer": {"left": {"heads": q.num_attention_heads, "kv_heads": q.num_key_value_heads,
+                                "dim": q.head_dim, "vdim": q.head_dim, "scale": q.head_dim ** -0.5,
+                                "mask": {"size": window, "keep_first": keep}},
+                       "left_scale": 1.0,
+                       "right": {"heads": r_heads, "dim": r_dim, "decay_rank": 64},
+                       "right_scale": 1.0},
+             "mlp": {"kind": "dense", "ff": q.intermediate_size}}
+    return GamilornConfig.from_dict({
+        "architecture": "Gamilorn", "vocab": q.vocab_size, "width": q.hidden_size,
+        "max_positions": 8192, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": [layer] * layers})
+
+
+def design_arm(a) -> int:
+    """``--design gamilorn``: prompt and decode throughput of the Gamilorn design at layer sizes of
+    real models (random weights, ``--design-layers`` layers), beside Qwen3 at the same sizes, and
+    the new design's kernels one by one beside the like kernels of Qwen3, each with its share of
+    the measured roofline.  Prints one JSON line of its own; the default benchmark is untouched."""
+    import torch
+
+    from deterministic_inference_b200 import EngineConfig, SamplingParams, preset
+    from deterministic_inference_b200.engine.batch import SequenceInput, build_step_batch
+    from deterministic_inference_b200.engine.engine import Engine
+    from deterministic_inference_b200.kernels import ops
+    from deterministic_inference_b200.sampling.sampler import sample
+
+    pk = peaks()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    gen = torch.Generator().manual_seed(1)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)     # > L2
+    greedy = SamplingParams(max_new_tokens=1 << 20, ignore_eos=True)
+    n_layers, n_prompt, ctx = a.design_layers, a.prefill_tokens, a.context
+    batches = sorted({int(x) for x in a.design_batches.split(",") if x.strip()})
+
+    def timed(fn, repeats=5):
+        """Median device time of ``fn`` in ms, L2 flushed before every run."""
+        out = []
+        for _ in range(repeats):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            out.append(s.elapsed_time(e))
+        return sorted(out)[len(out) // 2]
+
+    def prompt_of(vocab, n):
+        return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+    def engine_for(mcfg):
+        per_req = ctx + a.point_steps + a.warmup + 96
+        pool = max(batches) * (-(-per_req // 16) * 16) + n_prompt + 1024
+        return Engine(EngineConfig(model_config=mcfg, random_seed=0, dtype="bfloat16", kv_pool_tokens=pool,
+                                   page_size=16, max_reqs=max(batches) + 8, max_seq_len=8192,
+                                   max_prefill_tokens=8192, max_decode_batch=max(256, max(batches)),
+                                   device="cuda:0"))
+
+    def prefill_ms(engine, vocab):
+        runner, cache = engine.runner, engine.cache
+
+        def once(n):
+            slot = cache.allocate_slot()
+            toks = prompt_of(vocab, n)
+            ms = timed(lambda: runner.step([SequenceInput(slot, toks, 0, [n - 1])]), repeats=1)
+            cache.release_slot(slot)
+            return ms
+        once(n_prompt - 40)
+        return min(once(n_prompt) for _ in range(3))
+
+    def decode_ms(engine, vocab, batch):
+        runner, cache = engine.runner, engine.cache
+        slots = [cache.allocate_slot() for _ in range(batch)]
+        group = max(1, 8192 // ctx)
+        for i in range(0, batch, group):
+            runner.step([SequenceInput(s, prompt_of(vocab, ctx), 0, []) for s in slots[i:i + group]])
+        state = {"tokens": None}
+
+        def one(k):
+            pend = state["tokens"] is not None
+            entries = [SequenceInput(s, [0], ctx + k, [0], i if pend else -1) for i, s in enumerate(slots)]
+            logits, _ = runner.step(entries, state["tokens"])
+            state["tokens"] = sample(logits, [greedy] * batch, [ctx + k + 1] * batch)
+        for k in range(a.warmup):
+            one(k)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for k in range(a.warmup, a.warmup + a.point_steps):
+            one(k)
+        e.record()
+        torch.cuda.synchronize()
+        for sl in slots:
+            cache.release_slot(sl)
+        return s.elapsed_time(e) / a.point_steps
+
+    def kernel_rows(eng_g, eng_q, gcfg, qcfg):
+        """The new kernels and the like kernels of Qwen3 on one layer's shapes: a prompt of
+        ``n_prompt`` tokens, and a decode step of 8 requests with ``ctx`` cached tokens."""
+        rows = {}
+        hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        left = gcfg.layers[0]["mixer"]["left"]
+        right = gcfg.layers[0]["mixer"]["right"]
+        hq, hkv, d, w = left["heads"], left["kv_heads"], left["dim"], gcfg.width
+        win, keep = left["mask"]["size"], left["mask"]["keep_first"]
+        rh, rd, rank = right["heads"], right["dim"], right["decay_rank"]
+        bf = torch.bfloat16
+
+        def row(name, ms, nbytes, flops):
+            floor = max(nbytes / hbm, flops / tf) * 1e3
+            rows[name] = {"ms": round(ms, 4), "roofline_ms": round(floor, 4), "of_roofline": round(floor / ms, 4)}
+
+        for what, batch, q_len, before in (("prompt", 1, n_prompt, 0), ("decode_b8", 8, 1, ctx)):
+            t = batch * q_len
+            for eng, mine in ((eng_g, True), (eng_q, False)):
+                runner, cache = eng.runner, eng.cache
+                slots = [cache.allocate_slot() for _ in range(batch)]
+                if before:
+                    for sl in slots:
+                        runner.step([SequenceInput(sl, prompt_of(1000, before), 0, [])])
+                entries = [SequenceInput(sl, [1] * q_len, before, []) for sl in slots]
+                for e_ in entries:
+                    cache.allocate(e_.slot, before + q_len)
+                cache.reset_fresh_state()
+                step = build_step_batch(entries, cache, dev)
+                view = cache.view(0, step)
+                q = torch.randn(t, hq, d, device=dev).to(bf)
+                keys = batch * sum(min(p + 1, win + keep) if mine else p + 1 for p in range(before, before + q_len))
+                att_flops = 4 * keys * hq * d
+                att_bytes = 2 * (2 * t * hq * d + batch * hkv * 2 * d * min(before + q_len, (win + keep) if mine else 1 << 30))
+                if mine:
+                    kv = view.members[0]
+                    pb = torch.zeros(hq, device=dev)
+                    row(f"{what}: sigmoid attention", timed(lambda: ops.sigmoid_attention(
+                        q, kv.kv, kv.attention_meta, d ** -0.5, pb, d, kv.page_size, win, keep)), att_bytes, att_flops)
+                    width = 5 * rh * rd + rank
+                    proj = torch.randn(t, width, device=dev)
+                    w2 = (torch.randn(rank, rh * rd, device=dev) * 0.1).to(bf)
+                    vec = torch.zeros(rh * rd, device=dev)
+                    one = torch.ones(rh * rd, device=dev)
+                    state = view.members[1].state
+                    st_bytes = batch * rh * rd * rd * 4 * 2 + t * (width * 4 + rh * rd * 2)
+                    row(f"{what}: delta rule (prepare, recurrence, output)", timed(lambda: ops.delta_rule(
+                        proj, w2, vec, vec, one, state, step, rh, rd, rank, 0.6, 1e-6, 1e-6, bf)),
+                        st_bytes, 8 * t * rh * rd * rd)
+                    stream = torch.randn(t, w, device=dev)
+                    x0 = torch.randn(t, w, device=dev).to(bf)
+                    row(f"{what}: add + norm of the float32 stream (two terms)", timed(lambda: ops.stream_rms_norm(
+                        stream, one[:1].expand(w).contiguous(), 1e-6, bf, add=ops.WeightedSum([(1.0, x0), (1.0, x0)]))),
+                        t * w * (4 + 4 + 2 + 2 + 2), 0)
+                    z = torch.randn(t, gcfg.layers[0]["mlp"]["ff"], device=dev)
+                    row(f"{what}: xielu", timed(lambda: ops.xielu(z, 0.7, 1.2, bf)), z.numel() * 6, 0)
+                    qkv = torch.randn(t, (hq + 2 * hkv) * d, device=dev)
+                    bias = torch.zeros((hq + 2 * hkv) * d, device=dev)
+                    row(f"{what}: q/k/v bias + cache write", timed(lambda: ops.qkv_bias_cache(
+                        qkv, bias, hq, hkv, d, d, kv.kv, kv.slot_mapping, kv.page_size, bf)), qkv.numel() * 6, 0)
+                else:
+                    row(f"{what}: qwen3 softmax attention", timed(lambda: ops.paged_attention(
+                        q, view.kv, view.attention_meta, d ** -0.5, None)), att_bytes, att_flops)
+                    x0 = torch.randn(t, w, device=dev).to(bf)
+                    res = torch.randn(t, w, device=dev).to(bf)
+                    row(f"{what}: qwen3 add + norm", timed(lambda: ops.add_rms_norm(
+                        x0, res, torch.ones(w, device=dev), 1e-6)), t * w * 2 * 4, 0)
+                    gu = torch.randn(t, 2 * qcfg.intermediate_size, device=dev).to(bf)
+                    row(f"{what}: qwen3 silu gate", timed(lambda: ops.silu_mul(gu)), gu.numel() * 3, 0)
+                    qkv = torch.randn(t, (hq + 2 * hkv) * d, device=dev).to(bf)
+                    nw = torch.ones(d, device=dev)
+                    rope = runner.model.mixers[0].position_encoding.rotary_table()
+                    row(f"{what}: qwen3 q/k norm + rotation + cache write", timed(lambda: ops.qk_norm_rope_cache(
+                        qkv, hq, hkv, d, nw, nw, 1e-6, rope, step.positions, view.kv, view.slot_mapping,
+                        view.page_size)), qkv.numel() * 4, 0)
+                for sl in slots:
+                    cache.release_slot(sl)
+        return rows
+
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for name in [x for x in a.design_sizes.split(",") if x.strip()]:
+        preset_name, extra = DESIGN_SIZES[name]
+        qcfg = preset(preset_name, num_hidden_layers=n_layers, max_window_layers=n_layers)
+        gcfg = gamilorn_like(qcfg, n_layers, **extra)
+        out = {"layers": n_layers, "width": qcfg.hidden_size, "heads": f"{qcfg.num_attention_heads}/{qcfg.num_key_value_heads} x {qcfg.head_dim}",
+               "ff": qcfg.intermediate_size, "gamilorn": dict(extra, parameters=gcfg.num_parameters()),
+               "qwen3_parameters": qcfg.num_parameters()}
+        engines = {}
+        for label, mcfg in (("gamilorn", gcfg), ("qwen3", qcfg)):
+            eng = engines[label] = engine_for(mcfg)
+            ms = prefill_ms(eng, mcfg.vocab_size)
+            r = {"prefill_ms": round(ms, 3), "prefill_tok_s": round(n_prompt / (ms / 1e3))}
+            for b in batches:
+                dms = decode_ms(eng, mcfg.vocab_size, b)
+                r[f"decode_b{b}_ms"] = round(dms, 4)
+                r[f"decode_b{b}_tok_s"] = round(b / (dms / 1e3))
+            out[label + "_result"] = r
+        out["kernels"] = kernel_rows(engines["gamilorn"], engines["qwen3"], gcfg, qcfg)
+        sizes[name] = out
+        del engines
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "gamilorn beside qwen3 at equal layer sizes (bf16, 1 B200)", "impl": "ours",
+                      "dtype": "bf16", "data": "synthetic, random weights", "n_gpus": 1,
+                      "prompt_tokens": n_prompt, "decode_context": ctx, "decode_steps": a.point_steps,
+                      "warmup": a.warmup, "l2": "flushed before every timed kernel; steps hold more than L2",
+                      "peaks": pk, "clocks": sampler.stop(), "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -305,12 +528,20 @@ def main() -> int:
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="bracket this region with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); the numbers of such a run are not a result")
+    ap.add_argument("--design", default=None, choices=["gamilorn"],
+                    help="measure this design beside Qwen3 at equal layer sizes instead of the default "
+                         "workload (prints a line of its own)")
+    ap.add_argument("--design-sizes", default="0_6b,8b", help=f"of {sorted(DESIGN_SIZES)}")
+    ap.add_argument("--design-layers", type=int, default=4)
+    ap.add_argument("--design-batches", default="1,8,64")
     a = ap.parse_args()
 
     if a.warmup < 3:
         a.warmup = 3
     if a.impl == "reference":
         return reference_arm(a)
+    if a.design is not None:
+        return design_arm(a)
     if a.gpus != 1:
         print(f"bench.py measures one GPU only (this engine is single-GPU); --gpus {a.gpus} is not run")
         return 2

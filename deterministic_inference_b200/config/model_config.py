@@ -229,7 +229,7 @@ class Qwen3Config:
 
 
 # Named shapes (``--preset``) are data: one config.json-style file each under
-# ``presets/`` beside this module.  The engine itself only ever sees a Qwen3Config.
+# ``presets/`` beside this module.  The engine itself only ever sees a typed configuration.
 _PRESET_DIR = Path(__file__).resolve().parent / "presets"
 
 
@@ -237,10 +237,18 @@ def preset_names() -> list[str]:
     return sorted(p.stem for p in _PRESET_DIR.glob("*.json"))
 
 
-def preset(name: str, **overrides) -> Qwen3Config:
+def preset(name: str, **overrides):
+    """The typed configuration of a named shape: the class registered for the file's
+    ``architectures[0]`` or ``architecture`` (Qwen3 dense where it names none)."""
     path = _PRESET_DIR / f"{name}.json"
     if not path.exists():
         raise ConfigError(f"unknown preset {name!r}; known: {preset_names()}")
     d = json.loads(path.read_text())
     d.update(overrides)
-    return Qwen3Config.from_dict(d)
+    arch = (d.get("architectures") or [d.get("architecture") or "Qwen3ForCausalLM"])[0]
+    if arch == "Qwen3ForCausalLM":
+        return Qwen3Config.from_dict(d)
+    from ..models.registry import MODEL_REGISTRY      # (imported here: the registry imports this module)
+    if arch not in MODEL_REGISTRY:
+        raise ConfigError(f"preset {name!r} names the architecture {arch!r}, which is not registered")
+    return MODEL_REGISTRY[arch].from_dict(d)

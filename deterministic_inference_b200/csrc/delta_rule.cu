@@ -8,9 +8,10 @@
 
 #include "source.cuh"
 
-// proj row: [r | k | v | g | a_pre | lora hidden] = 5 * H * D + R columns.
+// proj row: [r | k | v | g | a_pre | lora hidden] = 5 * H * D + R columns; w2t [R][H * D] (the
+// decay map's second matrix, transposed: the threads of a block read consecutive elements).
 // packed [T][H][6][D] float32: w, a * u, u, k, r, v.
-__global__ void delta_prepare_kernel(Source proj, const void* w2, int w_dtype, const float* w0,
+__global__ void delta_prepare_kernel(Source proj, const void* w2t, int w_dtype, const float* w0,
                                      const float* a_bias, float* packed, int H, int D, int R,
                                      float decay_scale, float key_eps) {
   extern __shared__ float dp_smem[];     // [R] tanh of the lora hidden, then 32 floats of scratch
@@ -32,7 +33,7 @@ __global__ void delta_prepare_kernel(Source proj, const void* w2, int w_dtype, c
   const float ss = block_sum(k * k, scratch);      // (also orders the writes of th before their reads)
   if (c < D) {
     float z = 0.f;
-    for (int j = 0; j < R; ++j) z = __fmaf_rn(load_as(w2, w_dtype, (long long)ch * R + j), th[j], z);
+    for (int j = 0; j < R; ++j) z = __fmaf_rn(load_as(w2t, w_dtype, (long long)j * HD + ch), th[j], z);
     z = __fadd_rn(z, w0[ch]);
     w = expf(-decay_scale * sigmoid_f32(z));
     const float u = k / sqrtf(ss + key_eps);
@@ -46,24 +47,30 @@ __global__ void delta_prepare_kernel(Source proj, const void* w2, int w_dtype, c
   }
 }
 
-// One block per (sequence, head, 32 value columns); a column's D state rows are spread over
+// One warp per (sequence, head, 8 value columns); a column's D state rows are spread over
 // 4 lanes (row i = 16 q + 4 s + e for lane s), each lane keeping its rows in registers over
-// all tokens of the sequence in this step.  The two sums over the rows (u . S and r . S) are
-// added in ascending order inside a lane and then over the 4 lanes by a butterfly: an order
-// that depends on D alone.  The token's six vectors are staged in shared memory two tokens
-// deep by asynchronous copies.
-template <int MAXR>
+// all tokens of the sequence in this step.  Each of the two sums over the rows (u . S and
+// r . S) is taken as four chains inside a lane (rows e, e + 16, e + 32, ... for e = 0..3, in
+// ascending order), added as (c0 + c1) + (c2 + c3), and then over the 4 lanes by a butterfly:
+// an order that depends on D alone.  Every warp stages the token's six vectors in a ring of
+// its own in shared memory by asynchronous copies, DR_STAGES tokens deep, and waits for nobody
+// but itself.
+template <int MAXR, int DR_STAGES>
 __global__ void __launch_bounds__(128)
 delta_recurrence_kernel(const float* packed, float* state, float* o_out, const int* cu_q_lens,
                         const int* state_slots, int H, int D) {
-  extern __shared__ float dr_smem[];           // [2][6][Dp]
+  extern __shared__ __align__(16) float dr_smem[];           // [4 warps][DR_STAGES][6][Dp]
   const int Dp = (D + 15) / 16 * 16;
   const int NR = Dp / 4;                       // rows per lane (<= MAXR)
   const int b = blockIdx.x, h = blockIdx.y;
-  const int s = threadIdx.x & 3;
-  const int c = blockIdx.z * 32 + (threadIdx.x >> 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s = lane & 3;
+  const int c = (blockIdx.z * 4 + warp) * 8 + (lane >> 2);
   const bool active = c < D;
-  for (int i = threadIdx.x; i < 2 * 6 * Dp; i += blockDim.x) dr_smem[i] = 0.f;   // the padding stays 0
+  if ((blockIdx.z * 4 + warp) * 8 >= D) return;              // none of this warp's columns exists
+  float* ring = dr_smem + warp * DR_STAGES * 6 * Dp;
+  if (Dp != D)
+    for (int i = lane; i < DR_STAGES * 6 * Dp; i += 32) ring[i] = 0.f;   // the padding stays 0
   pdl_prologue();
   const int t0 = cu_q_lens[b], t1 = cu_q_lens[b + 1];
   if (t1 <= t0) return;
@@ -76,46 +83,63 @@ delta_recurrence_kernel(const float* packed, float* state, float* o_out, const i
     const int i = (ii >> 2) * 16 + s * 4 + (ii & 3);
     st[ii] = (kept && ii < NR && active && i < D) ? S[(long long)i * D + c] : 0.f;
   }
-  __syncthreads();
-  auto prefetch = [&](int t, int buf) {
-    const float* src = packed + ((long long)t * H + h) * 6 * D;
-    float* dst = dr_smem + buf * 6 * Dp;
-    for (int i = threadIdx.x; i < 6 * D; i += blockDim.x) {
-      const int vsel = i / D, d = i - vsel * D;
-      __pipeline_memcpy_async(dst + vsel * Dp + d, src + i, 4);
+  __syncwarp();
+  const bool wide = (D & 3) == 0;              // rows of D floats start on 16 bytes
+  // this lane's 16-byte pieces of a token's vectors: where they come from and go to
+  constexpr int PIECES = MAXR * 4 * 6 / 4 / 32;      // 6 * Dp / 4 pieces over 32 lanes, at most
+  int src_at[PIECES], dst_at[PIECES];
+#pragma unroll
+  for (int k = 0; k < PIECES; ++k) {
+    const int i = lane + 32 * k, per = D >> 2;
+    const int vsel = per ? i / per : 6, d4 = per ? i - vsel * per : 0;
+    src_at[k] = (wide && vsel < 6) ? vsel * D + d4 * 4 : -1;
+    dst_at[k] = vsel * Dp + d4 * 4;
+  }
+  auto prefetch = [&](int t, int stage) {
+    if (t < t1) {
+      const float* src = packed + ((long long)t * H + h) * 6 * D;
+      float* dst = ring + stage * 6 * Dp;
+      if (wide) {
+#pragma unroll
+        for (int k = 0; k < PIECES; ++k)
+          if (src_at[k] >= 0) __pipeline_memcpy_async(dst + dst_at[k], src + src_at[k], 16);
+      } else {
+        for (int i = lane; i < 6 * D; i += 32) {
+          const int vsel = i / D, d = i - vsel * D;
+          __pipeline_memcpy_async(dst + vsel * Dp + d, src + i, 4);
+        }
+      }
     }
-    __pipeline_commit();
+    __pipeline_commit();                       // (an empty group past the end keeps the count)
   };
-  prefetch(t0, 0);
+#pragma unroll
+  for (int k = 0; k < DR_STAGES - 1; ++k) prefetch(t0 + k, k);
   for (int t = t0; t < t1; ++t) {
-    const int buf = (t - t0) & 1;
-    if (t + 1 < t1) {
-      prefetch(t + 1, buf ^ 1);
-      __pipeline_wait_prior(1);
-    } else {
-      __pipeline_wait_prior(0);
-    }
-    __syncthreads();
-    const float* vw = dr_smem + buf * 6 * Dp;
+    const int stage = (t - t0) % DR_STAGES;
+    prefetch(t + DR_STAGES - 1, (stage + DR_STAGES - 1) % DR_STAGES);
+    __pipeline_wait_prior(DR_STAGES - 1);
+    __syncwarp();
+    const float* vw = ring + stage * 6 * Dp;
     const float* vb = vw + Dp;
     const float* vu = vb + Dp;
     const float* vk = vu + Dp;
     const float* vr = vk + Dp;
     const float v = active ? vr[Dp + c] : 0.f;
-    float dot = 0.f;
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
     for (int q = 0; q < MAXR / 4; ++q) {
       if (q * 4 < NR) {
         const float4 u4 = *reinterpret_cast<const float4*>(vu + q * 16 + s * 4);
-        dot = __fmaf_rn(u4.x, st[q * 4 + 0], dot);
-        dot = __fmaf_rn(u4.y, st[q * 4 + 1], dot);
-        dot = __fmaf_rn(u4.z, st[q * 4 + 2], dot);
-        dot = __fmaf_rn(u4.w, st[q * 4 + 3], dot);
+        d0 = __fmaf_rn(u4.x, st[q * 4 + 0], d0);
+        d1 = __fmaf_rn(u4.y, st[q * 4 + 1], d1);
+        d2 = __fmaf_rn(u4.z, st[q * 4 + 2], d2);
+        d3 = __fmaf_rn(u4.w, st[q * 4 + 3], d3);
       }
     }
+    float dot = __fadd_rn(__fadd_rn(d0, d1), __fadd_rn(d2, d3));
     dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, 1));
     dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, 2));
-    float o = 0.f;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
     for (int q = 0; q < MAXR / 4; ++q) {
       if (q * 4 < NR) {
@@ -129,16 +153,17 @@ delta_recurrence_kernel(const float* packed, float* state, float* o_out, const i
         float n2 = __fmaf_rn(k4.z, v, __fmaf_rn(-b4.z, dot, __fmul_rn(w4.z, st[q * 4 + 2])));
         float n3 = __fmaf_rn(k4.w, v, __fmaf_rn(-b4.w, dot, __fmul_rn(w4.w, st[q * 4 + 3])));
         st[q * 4 + 0] = n0; st[q * 4 + 1] = n1; st[q * 4 + 2] = n2; st[q * 4 + 3] = n3;
-        o = __fmaf_rn(r4.x, n0, o);
-        o = __fmaf_rn(r4.y, n1, o);
-        o = __fmaf_rn(r4.z, n2, o);
-        o = __fmaf_rn(r4.w, n3, o);
+        o0 = __fmaf_rn(r4.x, n0, o0);
+        o1 = __fmaf_rn(r4.y, n1, o1);
+        o2 = __fmaf_rn(r4.z, n2, o2);
+        o3 = __fmaf_rn(r4.w, n3, o3);
       }
     }
+    float o = __fadd_rn(__fadd_rn(o0, o1), __fadd_rn(o2, o3));
     o = __fadd_rn(o, __shfl_xor_sync(0xffffffffu, o, 1));
     o = __fadd_rn(o, __shfl_xor_sync(0xffffffffu, o, 2));
     if (active && s == 0) o_out[((long long)t * H + h) * D + c] = o;
-    __syncthreads();     // the next round's copies overwrite the other buffer, read one round ago
+    __syncwarp();        // the next round's copies overwrite the stage that was read one round ago
   }
 #pragma unroll
   for (int ii = 0; ii < MAXR; ++ii) {
@@ -164,26 +189,34 @@ __global__ void delta_output_kernel(const float* o, Source proj, const float* no
   }
 }
 
-template <int MAXR>
+template <int MAXR, int DR_STAGES>
 static int launch_recurrence(const float* packed, float* state, float* o_out, const int* cu_q_lens,
                              const int* state_slots, int B, int H, int D, cudaStream_t st) {
   const int Dp = (D + 15) / 16 * 16;
-  dib_launch(delta_recurrence_kernel<MAXR>, dim3(B, H, (D + 31) / 32), dim3(128),
-             sizeof(float) * 2 * 6 * Dp, st, packed, state, o_out, cu_q_lens, state_slots, H, D);
+  const size_t smem = sizeof(float) * 4 * DR_STAGES * 6 * Dp;      // 48 KB at D = 64, 72 at 128, 96 at 256
+  static DeviceOnce once;
+  if (smem > 48 * 1024 && !once.done()) {
+    if (cudaFuncSetAttribute(delta_recurrence_kernel<MAXR, DR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             100 * 1024) != cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    once.mark();
+  }
+  dib_launch(delta_recurrence_kernel<MAXR, DR_STAGES>, dim3(B, H, (D + 31) / 32), dim3(128), smem, st, packed, state,
+             o_out, cu_q_lens, state_slots, H, D);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
 
 extern "C" {
 
-int dib_delta_prepare(const void* proj, int kind, int splits, long long stride, const void* w2, int w_dtype,
+int dib_delta_prepare(const void* proj, int kind, int splits, long long stride, const void* w2t, int w_dtype,
                       const float* w0, const float* a_bias, float* packed, int T_, int H, int D, int R,
                       float decay_scale, float key_eps, cudaStream_t st) {
   if (T_ == 0) return DIB_OK;
   if (H < 1 || H > 65535 || D < 1 || D > 1024 || R < 0 || R > 8192) return DIB_BAD_SIZE;
   if (w_dtype != 0 && w_dtype != 1) return DIB_BAD_DTYPE;
   dib_launch(delta_prepare_kernel, dim3(T_, H), dim3((D + 31) / 32 * 32), sizeof(float) * (R + 32), st,
-             make_source(proj, kind, splits, stride), w2, w_dtype, w0, a_bias, packed, H, D, R, decay_scale,
+             make_source(proj, kind, splits, stride), w2t, w_dtype, w0, a_bias, packed, H, D, R, decay_scale,
              key_eps);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
@@ -196,9 +229,9 @@ int dib_delta_recurrence(const float* packed, float* state, float* o_out, const 
                          const int* state_slots, int B, int H, int D, cudaStream_t st) {
   if (B == 0) return DIB_OK;
   if (H < 1 || H > 65535 || D < 1 || D > 256) return DIB_BAD_SIZE;
-  if (D <= 64) return launch_recurrence<16>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
-  if (D <= 128) return launch_recurrence<32>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
-  return launch_recurrence<64>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+  if (D <= 64) return launch_recurrence<16, 8>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+  if (D <= 128) return launch_recurrence<32, 6>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+  return launch_recurrence<64, 4>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
 }
 
 int dib_delta_output(const float* o, const void* proj, int kind, int splits, long long stride,

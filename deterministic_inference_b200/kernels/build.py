@@ -50,7 +50,7 @@ EXTRA_HEADERS = {
     "decode_attention_noalloc": ("attention_bf16_kernels.cuh", "decode_attention_noalloc.h"),
     "attention_prefill_tc": ("attention_bf16_kernels.cuh",),
     "stream_f32": ("source.cuh",),
-    "sigmoid_attention": ("source.cuh",),
+    "sigmoid_attention": ("source.cuh", "sigmoid_attention_mma.cuh"),
     "delta_rule": ("source.cuh",),
 }
 

@@ -807,6 +807,25 @@ def qkv_bias_cache(qkv, bias, num_heads: int, num_kv_heads: int, head_dim: int, 
     return q
 
 
+# DIB200_SIGMOID_TC=0 (read once): bfloat16 steps run the float32-arithmetic kernel too
+SIGMOID_ATTENTION_TC = __import__("os").environ.get("DIB200_SIGMOID_TC", "1") != "0"
+
+
+def sigmoid_attention_tiles(q_lens: list, tokens_per_tile: int, device, first: int = 0) -> torch.Tensor:
+    """int32 [n, 3] on ``device``: (sequence, first token in the step, tokens) for every run of up
+    to ``tokens_per_tile`` consecutive tokens of one sequence, in the step's token order, for the
+    sequences from ``first`` on."""
+    rows, start = [], 0
+    for b, n in enumerate(q_lens):
+        for k in range(0, n if b >= first else 0, tokens_per_tile):
+            rows.append((b, start + k, min(tokens_per_tile, n - k)))
+        start += n
+    host = torch.tensor(rows, dtype=torch.int32).view(-1, 3)
+    if torch.device(device).type == "cuda":
+        return host.pin_memory().to(device, non_blocking=True)
+    return host
+
+
 def sigmoid_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float, head_bias,
                       v_head_dim: int, page_size: int, window=None, keep_first: int = 0) -> torch.Tensor:
     """[T, Hq, Dv]: every token's sum over its visible cached keys j of
@@ -828,6 +847,37 @@ def sigmoid_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: floa
     _need(meta.token_seq, "token_seq", torch.int32, 1)
     _need(meta.positions, "positions", torch.int32, 1)
     out = torch.empty(t, hq, v_head_dim, dtype=q.dtype, device=q.device)
+    win = int(window) if window else 0
+    if q.dtype == torch.bfloat16 and SIGMOID_ATTENTION_TC and d % 16 == 0 and v_head_dim % 16 == 0 \
+            and d <= 256 and v_head_dim <= 256 and hq // hkv <= 64 and getattr(meta, "q_lens", None) is not None \
+            and getattr(meta, "num_decode", None) is not None:
+        # the tensor-core form.  The step's leading one-token sequences (decoded tokens) go to
+        # CTAs whose warps share a tile's keys; the others to tiles of up to 64 (token,
+        # head-of-group) rows of one sequence, or of 128 where a sequence brings that many (the
+        # same bits either way).
+        group = hq // hkv
+        n_dec = meta.num_decode if group <= 16 else 0
+        rows = 128 if max(meta.q_lens[n_dec:], default=0) * group > 64 else 64
+        lists = meta.scratch.get(("sigmoid_attention_tiles", group, rows))
+        if lists is None:
+            lists = []
+            if n_dec:
+                lists.append((16, sigmoid_attention_tiles(meta.q_lens[:n_dec], 1, q.device)))
+            if n_dec < len(meta.q_lens):
+                lists.append((rows, sigmoid_attention_tiles(meta.q_lens, rows // group, q.device, first=n_dec)))
+            meta.scratch[("sigmoid_attention_tiles", group, rows)] = lists
+        st = 0
+        for form, tiles in lists:
+            st = _lib("sigmoid_attention").dib_sigmoid_attention_mma(
+                _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
+                _ptr(meta.positions), _ptr(meta.seq_lens), _ptr(tiles), c_int(tiles.shape[0]), _ptr(head_bias),
+                c_int(hq), c_int(hkv), c_int(d), c_int(v_head_dim), c_int(page_size), c_float(scale), c_int(win),
+                c_int(int(keep_first)), c_int(form), _stream())
+            if st in (-2, -3):
+                break
+            _check(st, "sigmoid_attention(tensor cores)", f"heads {hq}/{hkv}, sizes {d}/{v_head_dim}")
+        if st not in (-2, -3):
+            return out
     st = _lib("sigmoid_attention").dib_sigmoid_attention(
         _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
         _ptr(meta.token_seq), _ptr(meta.positions), _ptr(head_bias), c_int(t), c_int(hq), c_int(hkv), c_int(d),
@@ -839,24 +889,25 @@ def sigmoid_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: floa
 
 # ---------------------------------------------------------------- generalised delta rule
 
-def delta_rule(proj, w2: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: torch.Tensor,
+def delta_rule(proj, w2_t: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: torch.Tensor,
                state: torch.Tensor, step, num_heads: int, head_dim: int, lora_rank: int,
                decay_scale: float, key_eps: float, norm_eps: float, out_dtype) -> torch.Tensor:
     """The recurrence S_t = diag(w) S_(t-1) - (a * u)(u^T S_(t-1)) + k v^T, o_t = S_t^T r per head,
     over every sequence's tokens of the step, from and to ``state`` [slots, H, D, D] (float32,
     rows ``step.state_slots``); then each head's o over its root mean square, times
     ``norm_weight``, times sigmoid(g): [T, H * D] in ``out_dtype``.  ``proj`` rows are
-    [r | k | v | g | a | lora hidden]; w = exp(-decay_scale * sigmoid(w2 tanh(lora hidden) + w0)),
+    [r | k | v | g | a | lora hidden]; w = exp(-decay_scale * sigmoid(w2 tanh(lora hidden) + w0)) with
+    w2 given transposed (``w2_t`` [lora_rank, H * D]),
     a = sigmoid(a + a_bias), u = k / sqrt(sum(k^2) + key_eps)."""
     t, got = proj.shape
     hd = num_heads * head_dim
     if got != 5 * hd + lora_rank:
         raise KernelError(f"delta_rule: projection rows of {got}, expected {5 * hd + lora_rank}")
-    _need(w2, "w2", None, 2)
+    _need(w2_t, "w2_t", None, 2)
     _need(w0, "w0", torch.float32, 1)
     _need(norm_weight, "norm_weight", torch.float32, 1)
     _need(state, "state", torch.float32, 4)
-    if tuple(w2.shape) != (hd, lora_rank) or w0.shape[0] != hd or norm_weight.shape[0] != hd \
+    if tuple(w2_t.shape) != (lora_rank, hd) or w0.shape[0] != hd or norm_weight.shape[0] != hd \
             or tuple(state.shape[1:]) != (num_heads, head_dim, head_dim):
         raise KernelError("delta_rule: a weight or the state does not fit the head count and size")
     if a_bias is not None:
@@ -865,7 +916,7 @@ def delta_rule(proj, w2: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: to
     src = _source_args(proj)
     dev = state.device
     packed = torch.empty(t, num_heads, 6, head_dim, dtype=torch.float32, device=dev)
-    st = lib.dib_delta_prepare(*src, _ptr(w2), c_int(_dt(w2, "w2")), _ptr(w0), _ptr(a_bias), _ptr(packed),
+    st = lib.dib_delta_prepare(*src, _ptr(w2_t), c_int(_dt(w2_t, "w2_t")), _ptr(w0), _ptr(a_bias), _ptr(packed),
                                c_int(t), c_int(num_heads), c_int(head_dim), c_int(lora_rank),
                                c_float(decay_scale), c_float(key_eps), _stream())
     _check(st, "delta_rule(prepare)", f"heads {num_heads} of {head_dim}, rank {lora_rank}")

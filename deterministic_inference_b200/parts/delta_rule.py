@@ -42,7 +42,7 @@ class DeltaRule(Mixer):
                           norm="norm", o="o")
         self.names.update(names or {})
         self.out_dtype = ctx.dtype
-        self.w_in = self.w2 = self.w0 = self.a_bias = self.norm_weight = self.w_o = None
+        self.w_in = self.w2_t = self.w0 = self.a_bias = self.norm_weight = self.w_o = None
 
     def tensor_specs(self):
         p, n, w = self.prefix, self.names, self.hidden_size
@@ -60,7 +60,7 @@ class DeltaRule(Mixer):
         p, n = self.prefix, self.names
         # one product for everything that is read from x: [r | k | v | g | a | w1]
         self.w_in = torch.cat([tensors[p + n[x]] for x in ("r", "k", "v", "g", "a", "w1")], dim=0).contiguous()
-        self.w2, self.w0 = tensors[p + n["w2"]], tensors[p + n["w0"]]
+        self.w2_t, self.w0 = tensors[p + n["w2"]].t().contiguous(), tensors[p + n["w0"]]
         self.a_bias, self.norm_weight = tensors[p + n["a_bias"]], tensors[p + n["norm"]]
         self.w_o = tensors[p + n["o"]]
 
@@ -69,7 +69,7 @@ class DeltaRule(Mixer):
 
     def forward(self, x, step, cache):
         proj = ops.linear(x, self.w_in, out_dtype=torch.float32 if x.dtype != torch.float32 else None)
-        y = ops.delta_rule(proj, self.w2, self.w0, self.a_bias, self.norm_weight, cache.state, step,
+        y = ops.delta_rule(proj, self.w2_t, self.w0, self.a_bias, self.norm_weight, cache.state, step,
                            self.num_heads, self.head_dim, self.decay_rank, self.decay_scale, self.key_eps,
                            self.norm_eps, self.out_dtype)
         return ops.linear(y, self.w_o)

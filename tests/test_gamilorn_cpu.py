@@ -55,6 +55,21 @@ def test_the_decay_rank_comes_from_the_checkpoint(model_dirs, tmp_path):
     assert [l["mixer"]["right"]["decay_rank"] for l in cfg.layers] == [4, 8, 3]
 
 
+def test_a_preset_and_the_command_line_write_a_model_folder_the_registry_reads_back(tmp_path):
+    from deterministic_inference_b200.__main__ import main
+    from deterministic_inference_b200.config import preset
+
+    cfg = preset("gamilorn_tiny")
+    assert isinstance(cfg, GamilornConfig) and len(cfg.layers) == 3
+    assert main(["random", "--preset", "gamilorn_tiny", "--seed", "4", "--out", str(tmp_path / "m")]) == 0
+    back = config_from_dir(tmp_path / "m")
+    assert back.to_dict() == cfg.to_dict()
+    model = build_model(back, torch.bfloat16, "cpu")
+    tensors = load_weights(tmp_path / "m", model.tensor_specs(), model.plan, torch.bfloat16, "cpu")
+    assert tensors["l1.mix.right.w1"].shape == (8, 128) and "l1.norm2" not in tensors
+    assert tensors["l0.norm1"].dtype == torch.float32 and tensors["l0.mix.left.q"].dtype == torch.bfloat16
+
+
 @pytest.mark.parametrize("edit, text", [
     (lambda c: c.pop("width"), "width"),
     (lambda c: c["layers"][0].__setitem__("type", "serial"), "type"),

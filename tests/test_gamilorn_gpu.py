@@ -89,8 +89,10 @@ def paged(n_tokens_per_seq, page, generator):
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, page, window, keep", [
     (6, 2, 24, 40, 16, 37, 5),      # values wider than keys, a window that ends inside a page
     (4, 4, 16, 16, 8, None, 0),     # no window, one query head per key head
-    (8, 1, 32, 8, 16, 7, 19),       # more kept keys than the window is long
+    (8, 1, 32, 16, 16, 7, 19),      # more kept keys than the window is long
     (2, 1, 128, 64, 32, 64, 0),     # no kept keys, a window of two pages
+    (6, 2, 32, 48, 16, 37, 70),     # three heads to a group; kept keys beyond the first key tile
+    (5, 5, 64, 192, 16, 100, 3),    # wide values
 ])
 def test_sigmoid_attention_alone(dtype, heads, kv_heads, dim, vdim, page, window, keep):
     from deterministic_inference_b200.kernels import ops
@@ -130,6 +132,7 @@ def test_sigmoid_attention_alone(dtype, heads, kv_heads, dim, vdim, page, window
     steps = [[(0, 0, 90)], [(0, 90, 2), (1, 0, 31)], [(1, 31, 1), (0, 92, 13)], [(1, 32, 13), (0, 105, 41)]]
     steps += [[(0, p, 1)] for p in range(146, n)]
     got = [torch.zeros(n, heads, vdim, dtype=torch.float64), torch.zeros(n2, heads, vdim, dtype=torch.float64)]
+    q_stored = torch.zeros(n, heads, dim, dtype=dt, device=dev)      # the first sequence's q as the kernel left it
     for entries in steps:
         rows, seq_of, pos_of, slots = [], [], [], []
         for b, (s, start, count) in enumerate(entries):
@@ -143,16 +146,33 @@ def test_sigmoid_attention_alone(dtype, heads, kv_heads, dim, vdim, page, window
         x = torch.cat(rows) - bias                  # the kernel adds the bias back
         meta = SimpleNamespace(block_table=bt[[s for s, _, _ in entries]].contiguous().to(dev),
                                token_seq=torch.tensor(seq_of, dtype=torch.int32, device=dev),
-                               positions=torch.tensor(pos_of, dtype=torch.int32, device=dev))
+                               positions=torch.tensor(pos_of, dtype=torch.int32, device=dev),
+                               seq_lens=torch.tensor([st + c for _, st, c in entries], dtype=torch.int32, device=dev),
+                               q_lens=[c for _, _, c in entries], scratch={},
+                               num_decode=sum(1 for _, _, c in entries if c == 1))
         qd = ops.qkv_bias_cache(x.to(dev), bias.to(dev), heads, kv_heads, dim, vdim, cache,
                                 torch.tensor(slots, dtype=torch.int32, device=dev), page, dt)
         out = ops.sigmoid_attention(qd, cache, meta, scale, head_bias.to(dev), vdim, page, window, keep).cpu()
         at = 0
         for s, start, count in entries:
             got[s][start:start + count] = out[at:at + count].double()
+            if s == 0:
+                q_stored[start:start + count] = qd[at:at + count]
             at += count
     for s in (0, 1):
         close(got[s], want[s], dtype, f"attention of sequence {s}", f32=3e-5, bf16=8e-3)
+    # the same rows in one step: a row's bits do not depend on how the sequence was cut
+    meta = SimpleNamespace(block_table=bt[:1].contiguous().to(dev), token_seq=torch.zeros(n, dtype=torch.int32, device=dev),
+                           positions=torch.arange(n, dtype=torch.int32, device=dev),
+                           seq_lens=torch.tensor([n], dtype=torch.int32, device=dev), q_lens=[n], scratch={},
+                           num_decode=0)
+    whole = ops.sigmoid_attention(q_stored, cache, meta, scale, head_bias.to(dev), vdim, page, window, keep)
+    # (tokens that came alone ran on the kernel form for decoded tokens, which associates a
+    # row's sum over its keys differently: a rounding apart at most)
+    cut = 146 if dtype == "bfloat16" else n
+    assert torch.equal(whole.cpu().double()[:cut], got[0][:cut]), "a row's bits changed with the cutting"
+    if cut < n:
+        close(whole[cut:], got[0][cut:], dtype, "tokens alone against the same tokens in a prompt", bf16=4e-3)
     # the spikes did show: a wrong edge would move the last row by about 50
     assert float(want[0][last].abs().max()) > 50
 
@@ -200,7 +220,7 @@ def test_delta_rule_alone(dtype, heads, dim, rank):
         step = SimpleNamespace(cu_q_lens=torch.tensor(cu, dtype=torch.int32, device=dev),
                                state_slots=torch.tensor([slot_of[s] for s in who], dtype=torch.int32, device=dev),
                                num_seqs=len(who))
-        y = ops.delta_rule(x.to(dev), w2.to(dt).to(dev), w0.to(dev), a_bias.to(dev), norm_w.to(dev), state, step,
+        y = ops.delta_rule(x.to(dev), w2.to(dt).t().contiguous().to(dev), w0.to(dev), a_bias.to(dev), norm_w.to(dev), state, step,
                            heads, dim, rank, decay_scale, key_eps, eps, dt).cpu().double()
         for j, (s, c) in enumerate(zip(who, counts)):
             got[s][done[s]:done[s] + c] = y[cu[j]:cu[j + 1]]

@@ -274,7 +274,7 @@ def sigmoid_attention(q, kv_cache, meta, scale, head_bias, v_head_dim, page_size
     return out.to(q.dtype)
 
 
-def delta_rule(proj, w2, w0, a_bias, norm_weight, state, step, num_heads, head_dim, lora_rank,
+def delta_rule(proj, w2_t, w0, a_bias, norm_weight, state, step, num_heads, head_dim, lora_rank,
                decay_scale, key_eps, norm_eps, out_dtype):
     x = _plain(proj)
     t, hd = x.shape[0], num_heads * head_dim
@@ -284,7 +284,7 @@ def delta_rule(proj, w2, w0, a_bias, norm_weight, state, step, num_heads, head_d
     if a_bias is not None:
         a = a + a_bias
     a = torch.sigmoid(a).reshape(shape)
-    w = torch.exp(-decay_scale * torch.sigmoid(torch.tanh(x[:, 5 * hd:]) @ w2.float().T + w0)).reshape(shape)
+    w = torch.exp(-decay_scale * torch.sigmoid(torch.tanh(x[:, 5 * hd:]) @ w2_t.float() + w0)).reshape(shape)
     u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + key_eps)
     o = torch.zeros(shape)
     cu, slots = step.cu_q_lens.tolist(), step.state_slots.tolist()
