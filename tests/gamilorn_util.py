@@ -42,6 +42,13 @@ CONFIGS = {
         "norm": {"eps": 1e-5}, "logit_softcap": 12.0,
         "layers": [_layer(8, 4, 24, 16, 21, 13, 0.2, 1, 128, 6, 1.1, 0.8, 96),
                    _layer(2, 1, 48, 56, 100, 1, 0.15, 4, 8, 2, 0.6, 1.4, None)]}),
+    # sizes that are multiples of nothing: rows that start on no 16-byte border, key and value
+    # sizes the tensor-core kernel does not take, state heads of 18 (copies of 4 bytes), rank 3
+    "g4": dict(page_size=16, seed=24, config={
+        "architecture": "Gamilorn", "vocab": 131, "width": 100, "max_positions": 300,
+        "norm": {"eps": 1e-5}, "logit_softcap": 10.0,
+        "layers": [_layer(3, 3, 24, 40, 9, 2, 0.2, 5, 18, 3, 1.0, 1.0, 50),
+                   _layer(6, 2, 20, 12, 30, 7, 0.22, 2, 36, 5, 0.8, 0.9, None)]}),
 }
 
 

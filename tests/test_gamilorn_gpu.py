@@ -237,6 +237,7 @@ CASES = {
     "g1": ([1, 2, 17, 48, 131, 260], 31),
     "g2": ([5, 33, 64, 200], 32),
     "g3": ([3, 22, 57, 130, 333], 33),
+    "g4": ([1, 9, 40, 150], 34),
 }
 
 
