@@ -177,16 +177,21 @@ int dib_sigmoid_attention(const void* q, void* out, const void* cache, const int
 // The bfloat16 tensor-core form.  tiles: int32 [num_tiles][3] on the device = (sequence, first token
 // of the tile in the step, tokens), at most rows / (Hq / Hkv) tokens of consecutive positions each;
 // rows: 64 or 128 query rows to a CTA (the same bits either way), or 16: tiles of decoded tokens,
-// whose keys the CTA's four warps share.
+// whose keys the CTA's four warps share.  With rows 16 and partial != null (float32
+// [num_tokens, Hq, max_chunks, VD]; the tiles are then the step's first num_tokens tokens, one
+// each): a CTA per chunk of chunk_tiles key tiles and a second kernel that adds the chunks.
 // Takes D a multiple of 16 up to 256, VD a multiple of 16 up to 256, Hq / Hkv <= 64, 16-byte aligned
 // pointers; -2 otherwise (the caller runs the kernel above).
 int dib_sigmoid_attention_mma(const void* q, void* out, const void* cache, const int* block_table, int bt_width,
                               const int* positions, const int* seq_lens, const int* tiles, int num_tiles,
                               const float* head_bias, int Hq, int Hkv, int D, int VD, int page_size, float scale,
-                              int window, int keep_first, int rows, cudaStream_t st) {
+                              int window, int keep_first, int rows, float* partial, int chunk_tiles,
+                              int max_chunks, cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
   if (rows != 16 && rows != 64 && rows != 128) return DIB_BAD_SIZE;
   if (rows == 16 && Hq / Hkv > 16) return DIB_BAD_SIZE;
+  if (partial != nullptr && (rows != 16 || chunk_tiles < 1 || max_chunks < 1 || max_chunks > 65535))
+    return DIB_BAD_SIZE;
   if (Hq < 1 || Hkv < 1 || Hq % Hkv || Hq / Hkv > 64 || D < 16 || D % 16 || D > 256 || VD < 16 || VD % 16 ||
       VD > 256 || page_size < 1 || window < 0 || keep_first < 0 || Hkv > 65535)
     return DIB_BAD_SIZE;
@@ -196,14 +201,14 @@ int dib_sigmoid_attention_mma(const void* q, void* out, const void* cache, const
   return rows == 16                                                                                              \
              ? sa_mma::launch<NV, 16, true>(q, out, cache, block_table, bt_width, positions, seq_lens, tiles,    \
                                             num_tiles, head_bias, Hq, Hkv, D, VD, page_size, scale, window,      \
-                                            keep_first, st)                                                      \
+                                            keep_first, partial, chunk_tiles, max_chunks, num_tiles, st)         \
          : rows == 64                                                                                            \
              ? sa_mma::launch<NV, 64, false>(q, out, cache, block_table, bt_width, positions, seq_lens, tiles,   \
                                              num_tiles, head_bias, Hq, Hkv, D, VD, page_size, scale, window,     \
-                                             keep_first, st)                                                     \
+                                             keep_first, nullptr, 0, 1, 0, st)                                   \
              : sa_mma::launch<NV, 128, false>(q, out, cache, block_table, bt_width, positions, seq_lens, tiles,  \
                                               num_tiles, head_bias, Hq, Hkv, D, VD, page_size, scale, window,    \
-                                              keep_first, st)
+                                              keep_first, nullptr, 0, 1, 0, st)
   if (VD <= 64) SA_LAUNCH(4);
   if (VD <= 128) SA_LAUNCH(8);
   if (VD <= 192) SA_LAUNCH(12);

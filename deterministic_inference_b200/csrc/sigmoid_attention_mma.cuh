@@ -10,8 +10,10 @@
 //
 // KSPLIT (tiles of at most 16 rows: decoded tokens): the four warps share the 16 rows and
 // each takes 16 of a tile's 64 keys; at the end the warps' sums are added in warp order.  A
-// row's sum over its keys is then associated differently than in the other form (by a
-// rounding of float32), again in a way that depends on its position alone.
+// token's key tiles (in the order they are walked) are cut into chunks of `chunk_tiles`, a CTA
+// per chunk (blockIdx.z), each writing its float32 sums; a second kernel adds a row's chunks
+// in chunk order.  A row's sum over its keys is then associated differently than in the other
+// form (by roundings of float32), again in a way that depends on its position alone.
 #pragma once
 
 #include <cuda_pipeline.h>
@@ -65,7 +67,8 @@ __global__ void __launch_bounds__(KSPLIT ? 128 : ROWS * 2)
 sigmoid_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat16* cache,
                              const int* block_table, int bt_width, const int* positions, const int* seq_lens,
                              const int* tiles, const float* head_bias, int Hq, int Hkv, int D, int VD,
-                             int page_size, float scale, int window, int keep_first) {
+                             int page_size, float scale, int window, int keep_first, float* partial,
+                             int chunk_tiles, int max_chunks) {
   extern __shared__ __align__(16) unsigned char sam_smem[];
   const int R = Hq / Hkv;
   const int qs = D + PAD, vs = VD + PAD;                 // row strides in elements
@@ -87,15 +90,6 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const _
   const int* bt = block_table + (long long)b * bt_width;
   const long long page_elems = (long long)Hkv * page_size * (D + VD);
 
-  // Q rows: row r = token r / R, head g * R + r % R
-  const int dchunks = D / 8;
-  for (int idx = threadIdx.x; idx < ROWS * dchunks; idx += blockDim.x) {
-    const int r = idx / dchunks, ch = idx - r * dchunks;
-    const bool ok = r < rows_used;
-    const int tl = ok ? r / R : 0, hh = ok ? r % R : 0;
-    copy16(Qs + r * qs + ch * 8, q + ((long long)(t0 + tl) * Hq + g * R + hh) * D + ch * 8, ok);
-  }
-
   // key tiles: those of the kept first keys below the window, then those of the windows
   const int lo_min = window > 0 ? (pos0 - window + 1 > 0 ? pos0 - window + 1 : 0) : 0;
   const int w_first = lo_min / KT, w_last = pos_last / KT;
@@ -105,11 +99,26 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const _
     if (kept_tiles > w_first) kept_tiles = w_first;
   }
   const int n_tiles = kept_tiles + (w_last - w_first + 1);
+  // the tiles this CTA walks: all of them, or its chunk of them
+  const int chunk = (KSPLIT && partial != nullptr) ? blockIdx.z : 0;
+  const int it_begin = chunk * ((KSPLIT && partial != nullptr) ? chunk_tiles : 0);
+  const int it_end = (KSPLIT && partial != nullptr && it_begin + chunk_tiles < n_tiles) ? it_begin + chunk_tiles
+                                                                                      : n_tiles;
+  if (it_begin >= n_tiles) return;          // (the whole CTA: no such chunk at this position)
+
+  // Q rows: row r = token r / R, head g * R + r % R
+  const int dchunks = D / 8;
+  for (int idx = threadIdx.x; idx < ROWS * dchunks; idx += blockDim.x) {
+    const int r = idx / dchunks, ch = idx - r * dchunks;
+    const bool ok = r < rows_used;
+    const int tl = ok ? r / R : 0, hh = ok ? r % R : 0;
+    copy16(Qs + r * qs + ch * 8, q + ((long long)(t0 + tl) * Hq + g * R + hh) * D + ch * 8, ok);
+  }
   auto tile_at = [&](int it) { return it < kept_tiles ? it : w_first + (it - kept_tiles); };
 
   const int vchunks = VD / 8;
   auto find_rows = [&](int it) {          // by the first KT threads, for tile `it` (if there is one)
-    if (threadIdx.x < KT && it < n_tiles) {
+    if (threadIdx.x < KT && it < it_end) {
       const int j = tile_at(it) * KT + threadIdx.x;
       long long ko = -1, vo = -1;
       if (j < kv_len) {
@@ -160,13 +169,13 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const _
 #pragma unroll
   for (int n = 0; n < NV16 * 2; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
-  find_rows(0);
-  find_rows(1);
+  find_rows(it_begin);
+  find_rows(it_begin + 1);
   __syncthreads();
-  load_tile(0, 0);
-  for (int it = 0; it < n_tiles; ++it) {
+  load_tile(it_begin, it_begin & 1);
+  for (int it = it_begin; it < it_end; ++it) {
     const int stage = it & 1;
-    if (it + 1 < n_tiles) {
+    if (it + 1 < it_end) {
       load_tile(it + 1, stage ^ 1);
       find_rows(it + 2);        // into this tile's entries: its copies were issued a round ago
       __pipeline_wait_prior(1);
@@ -257,7 +266,9 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const _
       float v = part[r * VD + col];
 #pragma unroll
       for (int w = 1; w < 4; ++w) v = __fadd_rn(v, part[(w * 16 + r) * VD + col]);
-      out[((long long)(t0 + r / R) * Hq + g * R + r % R) * VD + col] = __float2bfloat16_rn(v);
+      const long long row = (long long)(t0 + r / R) * Hq + g * R + r % R;
+      if (partial != nullptr) partial[(row * max_chunks + chunk) * VD + col] = v;
+      else out[row * VD + col] = __float2bfloat16_rn(v);
     }
   } else {
 #pragma unroll
@@ -276,6 +287,32 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const _
   }
 }
 
+// out[t, h, :] = the sum of the row's chunks in chunk order; a token at position p has
+// ceil(tiles(p) / chunk_tiles) chunks, tiles(p) as the kernel above counts them.
+__global__ void sigmoid_attention_merge_kernel(const float* partial, __nv_bfloat16* out, const int* positions,
+                                               int Hq, int VD, int window, int keep_first, int chunk_tiles,
+                                               int max_chunks) {
+  pdl_prologue();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int pos = positions[t];
+  const int lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+  const int w_first = lo / KT, w_last = pos / KT;
+  int kept_tiles = 0;
+  if (window > 0 && keep_first > 0) {
+    kept_tiles = (keep_first + KT - 1) / KT;
+    if (kept_tiles > w_first) kept_tiles = w_first;
+  }
+  const int n_tiles = kept_tiles + (w_last - w_first + 1);
+  int chunks = (n_tiles + chunk_tiles - 1) / chunk_tiles;
+  if (chunks > max_chunks) chunks = max_chunks;
+  const long long row = (long long)t * Hq + h;
+  for (int col = threadIdx.x; col < VD; col += blockDim.x) {
+    float v = partial[(row * max_chunks) * VD + col];
+    for (int c = 1; c < chunks; ++c) v = __fadd_rn(v, partial[(row * max_chunks + c) * VD + col]);
+    out[row * VD + col] = __float2bfloat16_rn(v);
+  }
+}
+
 static inline size_t smem_bytes(int D, int VD, int rows) {
   return sizeof(__nv_bfloat16) * ((size_t)rows * (D + PAD) + 2 * (size_t)KT * (D + PAD) + 2 * (size_t)KT * (VD + PAD));
 }
@@ -284,8 +321,10 @@ template <int NV16, int ROWS, bool KSPLIT>
 static int launch(const void* q, void* out, const void* cache, const int* block_table, int bt_width,
                   const int* positions, const int* seq_lens, const int* tiles, int num_tiles,
                   const float* head_bias, int Hq, int Hkv, int D, int VD, int page_size, float scale, int window,
-                  int keep_first, cudaStream_t st) {
+                  int keep_first, float* partial, int chunk_tiles, int max_chunks, int num_tokens,
+                  cudaStream_t st) {
   const size_t smem = smem_bytes(D, VD, ROWS);
+  const bool chunked = KSPLIT && partial != nullptr;
   static DeviceOnce once;
   if (!once.done()) {
     if (cudaFuncSetAttribute(sigmoid_attention_mma_kernel<NV16, ROWS, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -293,10 +332,17 @@ static int launch(const void* q, void* out, const void* cache, const int* block_
       return DIB_LAUNCH_FAILED;
     once.mark();
   }
-  dib_launch(sigmoid_attention_mma_kernel<NV16, ROWS, KSPLIT>, dim3(num_tiles, Hkv), dim3(KSPLIT ? 128 : ROWS * 2), smem, st,
-             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, block_table, bt_width,
-             positions, seq_lens, tiles, head_bias, Hq, Hkv, D, VD, page_size, scale, window, keep_first);
+  dib_launch(sigmoid_attention_mma_kernel<NV16, ROWS, KSPLIT>, dim3(num_tiles, Hkv, chunked ? max_chunks : 1),
+             dim3(KSPLIT ? 128 : ROWS * 2), smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+             (const __nv_bfloat16*)cache, block_table, bt_width, positions, seq_lens, tiles, head_bias, Hq, Hkv, D,
+             VD, page_size, scale, window, keep_first, chunked ? partial : (float*)nullptr, chunk_tiles, max_chunks);
   DIB_CHECK_LAUNCH();
+  if (chunked) {
+    dib_launch(sigmoid_attention_merge_kernel, dim3(num_tokens, Hq), dim3(VD >= 128 ? 128 : 64), 0, st,
+               (const float*)partial, (__nv_bfloat16*)out, positions, Hq, VD, window, keep_first, chunk_tiles,
+               max_chunks);
+    DIB_CHECK_LAUNCH();
+  }
   return DIB_OK;
 }
 

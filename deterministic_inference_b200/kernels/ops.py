@@ -809,6 +809,9 @@ def qkv_bias_cache(qkv, bias, num_heads: int, num_kv_heads: int, head_dim: int, 
 
 # DIB200_SIGMOID_TC=0 (read once): bfloat16 steps run the float32-arithmetic kernel too
 SIGMOID_ATTENTION_TC = __import__("os").environ.get("DIB200_SIGMOID_TC", "1") != "0"
+# key tiles of 64 keys per CTA of a decoded token (a constant: where a token's sum over its
+# keys is cut depends on its position alone)
+SIGMOID_DECODE_CHUNK_TILES = 4
 
 
 def sigmoid_attention_tiles(q_lens: list, tokens_per_tile: int, device, first: int = 0) -> torch.Tensor:
@@ -850,7 +853,7 @@ def sigmoid_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: floa
     win = int(window) if window else 0
     if q.dtype == torch.bfloat16 and SIGMOID_ATTENTION_TC and d % 16 == 0 and v_head_dim % 16 == 0 \
             and d <= 256 and v_head_dim <= 256 and hq // hkv <= 64 and getattr(meta, "q_lens", None) is not None \
-            and getattr(meta, "num_decode", None) is not None:
+            and getattr(meta, "num_decode", None) is not None and getattr(meta, "kv_lens", None) is not None:
         # the tensor-core form.  The step's leading one-token sequences (decoded tokens) go to
         # CTAs whose warps share a tile's keys; the others to tiles of up to 64 (token,
         # head-of-group) rows of one sequence, or of 128 where a sequence brings that many (the
@@ -868,11 +871,22 @@ def sigmoid_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: floa
             meta.scratch[("sigmoid_attention_tiles", group, rows)] = lists
         st = 0
         for form, tiles in lists:
+            partial, max_chunks = None, 1
+            if form == 16:
+                # a decoded token's key tiles in chunks, a CTA each: the most tiles a token can have
+                if win:
+                    most = -(-int(keep_first) // 64) + win // 64 + 2
+                else:
+                    most = max(meta.kv_lens[:n_dec]) // 64 + 1
+                max_chunks = -(-most // SIGMOID_DECODE_CHUNK_TILES)
+                if max_chunks > 1:
+                    partial = torch.empty(n_dec, hq, max_chunks, v_head_dim, dtype=torch.float32, device=q.device)
             st = _lib("sigmoid_attention").dib_sigmoid_attention_mma(
                 _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
                 _ptr(meta.positions), _ptr(meta.seq_lens), _ptr(tiles), c_int(tiles.shape[0]), _ptr(head_bias),
                 c_int(hq), c_int(hkv), c_int(d), c_int(v_head_dim), c_int(page_size), c_float(scale), c_int(win),
-                c_int(int(keep_first)), c_int(form), _stream())
+                c_int(int(keep_first)), c_int(form), _ptr(partial), c_int(SIGMOID_DECODE_CHUNK_TILES),
+                c_int(max_chunks), _stream())
             if st in (-2, -3):
                 break
             _check(st, "sigmoid_attention(tensor cores)", f"heads {hq}/{hkv}, sizes {d}/{v_head_dim}")

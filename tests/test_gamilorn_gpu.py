@@ -148,8 +148,8 @@ def test_sigmoid_attention_alone(dtype, heads, kv_heads, dim, vdim, page, window
                                token_seq=torch.tensor(seq_of, dtype=torch.int32, device=dev),
                                positions=torch.tensor(pos_of, dtype=torch.int32, device=dev),
                                seq_lens=torch.tensor([st + c for _, st, c in entries], dtype=torch.int32, device=dev),
-                               q_lens=[c for _, _, c in entries], scratch={},
-                               num_decode=sum(1 for _, _, c in entries if c == 1))
+                               q_lens=[c for _, _, c in entries], kv_lens=[st + c for _, st, c in entries],
+                               scratch={}, num_decode=sum(1 for _, _, c in entries if c == 1))
         qd = ops.qkv_bias_cache(x.to(dev), bias.to(dev), heads, kv_heads, dim, vdim, cache,
                                 torch.tensor(slots, dtype=torch.int32, device=dev), page, dt)
         out = ops.sigmoid_attention(qd, cache, meta, scale, head_bias.to(dev), vdim, page, window, keep).cpu()
@@ -164,8 +164,8 @@ def test_sigmoid_attention_alone(dtype, heads, kv_heads, dim, vdim, page, window
     # the same rows in one step: a row's bits do not depend on how the sequence was cut
     meta = SimpleNamespace(block_table=bt[:1].contiguous().to(dev), token_seq=torch.zeros(n, dtype=torch.int32, device=dev),
                            positions=torch.arange(n, dtype=torch.int32, device=dev),
-                           seq_lens=torch.tensor([n], dtype=torch.int32, device=dev), q_lens=[n], scratch={},
-                           num_decode=0)
+                           seq_lens=torch.tensor([n], dtype=torch.int32, device=dev), q_lens=[n], kv_lens=[n],
+                           scratch={}, num_decode=0)
     whole = ops.sigmoid_attention(q_stored, cache, meta, scale, head_bias.to(dev), vdim, page, window, keep)
     # (tokens that came alone ran on the kernel form for decoded tokens, which associates a
     # row's sum over its keys differently: a rounding apart at most)
