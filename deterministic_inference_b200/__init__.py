@@ -1,4 +1,5 @@
-"""A small, whole, single-GPU inference engine for Qwen3 dense on B200 (sm_100a):
+"""A small, whole, single-GPU inference engine for Qwen3 dense (and a second design, Gamilorn,
+registered beside it) on B200 (sm_100a):
 typed configuration and registry, safetensors weights, a model put together from
 parts, a paged cache manager, one step function over mixed batches, a
 continuous-batching scheduler, sampling, and hand-written CUDA kernels.
@@ -7,9 +8,10 @@ continuous-batching scheduler, sampling, and hand-written CUDA kernels.
     out = Engine(EngineConfig(model_path=DIR)).generate([[1, 2, 3]], SamplingParams())
 """
 
-from .config import ConfigError, EngineConfig, Qwen3Config, SamplingParams, preset, preset_names
+from .config import (ConfigError, EngineConfig, GamilornConfig, Qwen3Config, SamplingParams, preset,
+                     preset_names)
 
-__all__ = ["Engine", "EngineConfig", "SamplingParams", "Qwen3Config", "ConfigError", "preset",
+__all__ = ["Engine", "EngineConfig", "SamplingParams", "Qwen3Config", "GamilornConfig", "ConfigError", "preset",
            "preset_names", "RequestOutput"]
 
 
