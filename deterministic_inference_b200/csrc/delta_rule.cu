@@ -71,7 +71,7 @@ delta_recurrence_kernel(const float* packed, float* state, float* o_out, const i
   float* ring = dr_smem + warp * DR_STAGES * 6 * Dp;
   if (Dp != D)
     for (int i = lane; i < DR_STAGES * 6 * Dp; i += 32) ring[i] = 0.f;   // the padding stays 0
-  pdl_prologue();
+  pdl_wait();                        // (the kernel behind this one is not launched ahead of its end)
   const int t0 = cu_q_lens[b], t1 = cu_q_lens[b + 1];
   if (t1 <= t0) return;
   const long long slot = state_slots[b];
@@ -172,6 +172,144 @@ delta_recurrence_kernel(const float* packed, float* state, float* o_out, const i
   }
 }
 
+// The same recurrence with a column's rows over 16 lanes (row i = 64 q + 4 s + e for lane s): a
+// block of four warps per (sequence, head, 8 value columns), two columns a warp, the token's
+// vectors staged once per block, DR_STAGES tokens deep, one barrier a token, the block's slab of
+// the state through shared memory in rows of 32 bytes.  Fewer instructions per token and warp
+// (4 rows a lane at D = 64) and four times the CTAs: the form for steps with few sequences and
+// many tokens (prompt portions).  Its sums are ordered differently from the form above (four
+// chains by e, then a butterfly over 16 lanes), again by D alone.
+template <int MAXR, int DR_STAGES>
+__global__ void __launch_bounds__(128)
+delta_recurrence_wide_kernel(const float* packed, float* state, float* o_out, const int* cu_q_lens,
+                             const int* state_slots, int H, int D) {
+  extern __shared__ __align__(16) float dr_smem[];           // [DR_STAGES][6][Dp]; first also [D][8] of state
+  const int Dp = (D + 63) / 64 * 64;
+  const int NR = Dp / 16;                      // rows per lane (<= MAXR)
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s = lane & 15;
+  const int cl = warp * 2 + (lane >> 4);       // this lane's column among the block's 8
+  const int c0 = blockIdx.z * 8, c = c0 + cl;
+  const bool active = c < D;
+  pdl_wait();                        // (launched in stream order; nothing is launched ahead of its end either)
+  const int t0 = cu_q_lens[b], t1 = cu_q_lens[b + 1];
+  if (t1 <= t0) return;
+  const long long slot = state_slots[b];
+  const bool kept = slot != 0;       // slot 0 belongs to padding sequences: zero state, nothing stored
+  float* S = state + ((slot * H + h) * D) * (long long)D;
+  float* slab = dr_smem;                        // [D][8]
+  for (int i = threadIdx.x; i < D * 8; i += blockDim.x) {
+    const int row = i >> 3, col = i & 7;
+    slab[i] = (kept && c0 + col < D) ? S[(long long)row * D + c0 + col] : 0.f;
+  }
+  __syncthreads();
+  float st[MAXR];
+#pragma unroll
+  for (int ii = 0; ii < MAXR; ++ii) {
+    const int i = (ii >> 2) * 64 + s * 4 + (ii & 3);
+    st[ii] = (ii < NR && i < D) ? slab[i * 8 + cl] : 0.f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < DR_STAGES * 6 * Dp; i += blockDim.x) dr_smem[i] = 0.f;   // the padding stays 0
+  __syncthreads();
+  const bool wide = (D & 3) == 0;              // rows of D floats start on 16 bytes
+  // this thread's 16-byte piece of a token's vectors (6 * D / 4 pieces over 128 threads: at most 3)
+  int src_at[3], dst_at[3];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const int i = threadIdx.x + 128 * k, per = D >> 2;
+    const int vsel = per ? i / per : 6, d4 = per ? i - vsel * per : 0;
+    src_at[k] = (wide && vsel < 6) ? vsel * D + d4 * 4 : -1;
+    dst_at[k] = vsel * Dp + d4 * 4;
+  }
+  auto prefetch = [&](int t, int stage) {
+    if (t < t1) {
+      const float* src = packed + ((long long)t * H + h) * 6 * D;
+      float* dst = dr_smem + stage * 6 * Dp;
+      if (wide) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+          if (src_at[k] >= 0) __pipeline_memcpy_async(dst + dst_at[k], src + src_at[k], 16);
+      } else {
+        for (int i = threadIdx.x; i < 6 * D; i += blockDim.x) {
+          const int vsel = i / D, d = i - vsel * D;
+          __pipeline_memcpy_async(dst + vsel * Dp + d, src + i, 4);
+        }
+      }
+    }
+    __pipeline_commit();                       // (an empty group past the end keeps the count)
+  };
+#pragma unroll
+  for (int k = 0; k < DR_STAGES - 1; ++k) prefetch(t0 + k, k);
+  float* o_at = o_out + ((long long)t0 * H + h) * D + c;
+  const long long o_step = (long long)H * D;
+  for (int t = t0; t < t1; ++t) {
+    const int stage = (t - t0) % DR_STAGES;
+    __pipeline_wait_prior(DR_STAGES - 2);      // this thread's copies of token t have landed
+    __syncthreads();                           // ... and everybody's; everybody is done with token t - 1
+    prefetch(t + DR_STAGES - 1, (stage + DR_STAGES - 1) % DR_STAGES);     // into the stage of token t - 1
+    const float* vw = dr_smem + stage * 6 * Dp;
+    const float* vb = vw + Dp;
+    const float* vu = vb + Dp;
+    const float* vk = vu + Dp;
+    const float* vr = vk + Dp;
+    const float v = active ? vr[Dp + c] : 0.f;
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+    for (int q = 0; q < MAXR / 4; ++q) {
+      if (q * 4 < NR) {
+        const float4 u4 = *reinterpret_cast<const float4*>(vu + q * 64 + s * 4);
+        d0 = __fmaf_rn(u4.x, st[q * 4 + 0], d0);
+        d1 = __fmaf_rn(u4.y, st[q * 4 + 1], d1);
+        d2 = __fmaf_rn(u4.z, st[q * 4 + 2], d2);
+        d3 = __fmaf_rn(u4.w, st[q * 4 + 3], d3);
+      }
+    }
+    float dot = __fadd_rn(__fadd_rn(d0, d1), __fadd_rn(d2, d3));
+#pragma unroll
+    for (int m = 1; m < 16; m <<= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, m));
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int q = 0; q < MAXR / 4; ++q) {
+      if (q * 4 < NR) {
+        const int at = q * 64 + s * 4;
+        const float4 w4 = *reinterpret_cast<const float4*>(vw + at);
+        const float4 b4 = *reinterpret_cast<const float4*>(vb + at);
+        const float4 k4 = *reinterpret_cast<const float4*>(vk + at);
+        const float4 r4 = *reinterpret_cast<const float4*>(vr + at);
+        float n0 = __fmaf_rn(k4.x, v, __fmaf_rn(-b4.x, dot, __fmul_rn(w4.x, st[q * 4 + 0])));
+        float n1 = __fmaf_rn(k4.y, v, __fmaf_rn(-b4.y, dot, __fmul_rn(w4.y, st[q * 4 + 1])));
+        float n2 = __fmaf_rn(k4.z, v, __fmaf_rn(-b4.z, dot, __fmul_rn(w4.z, st[q * 4 + 2])));
+        float n3 = __fmaf_rn(k4.w, v, __fmaf_rn(-b4.w, dot, __fmul_rn(w4.w, st[q * 4 + 3])));
+        st[q * 4 + 0] = n0; st[q * 4 + 1] = n1; st[q * 4 + 2] = n2; st[q * 4 + 3] = n3;
+        o0 = __fmaf_rn(r4.x, n0, o0);
+        o1 = __fmaf_rn(r4.y, n1, o1);
+        o2 = __fmaf_rn(r4.z, n2, o2);
+        o3 = __fmaf_rn(r4.w, n3, o3);
+      }
+    }
+    float o = __fadd_rn(__fadd_rn(o0, o1), __fadd_rn(o2, o3));
+#pragma unroll
+    for (int m = 1; m < 16; m <<= 1) o = __fadd_rn(o, __shfl_xor_sync(0xffffffffu, o, m));
+    if (active && s == 0) *o_at = o;
+    o_at += o_step;
+  }
+  __pipeline_wait_prior(0);
+  __syncthreads();                   // the ring is free: the slab goes out through it
+#pragma unroll
+  for (int ii = 0; ii < MAXR; ++ii) {
+    const int i = (ii >> 2) * 64 + s * 4 + (ii & 3);
+    if (ii < NR && i < D) slab[i * 8 + cl] = st[ii];
+  }
+  __syncthreads();
+  if (kept)
+    for (int i = threadIdx.x; i < D * 8; i += blockDim.x) {
+      const int row = i >> 3, col = i & 7;
+      if (c0 + col < D) S[(long long)row * D + c0 + col] = slab[i];
+    }
+}
+
 // y[t, h, :] = o / sqrt(mean(o^2) + eps) * norm_w[h, :] * sigmoid(g[t, h, :])
 __global__ void delta_output_kernel(const float* o, Source proj, const float* norm_w, void* out, int out_dtype,
                                     int H, int D, int R, float eps) {
@@ -207,6 +345,27 @@ static int launch_recurrence(const float* packed, float* state, float* o_out, co
   return DIB_OK;
 }
 
+template <int MAXR, int DR_STAGES>
+static int launch_recurrence_wide(const float* packed, float* state, float* o_out, const int* cu_q_lens,
+                                  const int* state_slots, int B, int H, int D, cudaStream_t st) {
+  const int Dp = (D + 63) / 64 * 64;
+  size_t smem = sizeof(float) * DR_STAGES * 6 * Dp;              // 12 KB at D = 64, 24 at 256
+  if (smem < sizeof(float) * 8 * D) smem = sizeof(float) * 8 * D;
+  // Launched in plain stream order, not ahead of its predecessor's end: blocks that are placed
+  // while the kernel before still fills the GPU land several to an SM on the SMs that happen to
+  // be free, and a long chain of dependent instructions then shares its scheduler for the whole
+  // kernel (2,048 tokens, 16 heads of 64: 2.0 ms against 1.0 ms).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(B, H, (D + 7) / 8);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchKernelEx(&cfg, delta_recurrence_wide_kernel<MAXR, DR_STAGES>, packed, state, o_out, cu_q_lens,
+                     state_slots, H, D);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
 extern "C" {
 
 int dib_delta_prepare(const void* proj, int kind, int splits, long long stride, const void* w2t, int w_dtype,
@@ -225,10 +384,16 @@ int dib_delta_prepare(const void* proj, int kind, int splits, long long stride, 
 // state [slots, H, D, D] float32; sequence b of the step owns tokens cu_q_lens[b] .. cu_q_lens[b+1]-1
 // and the state slot state_slots[b].  Slot 0 is no request's: a sequence on it starts from a
 // zero state and leaves none.
+// form 1: a column's rows over 16 lanes (for steps of few sequences with many tokens), 0: over 4.
 int dib_delta_recurrence(const float* packed, float* state, float* o_out, const int* cu_q_lens,
-                         const int* state_slots, int B, int H, int D, cudaStream_t st) {
+                         const int* state_slots, int B, int H, int D, int form, cudaStream_t st) {
   if (B == 0) return DIB_OK;
   if (H < 1 || H > 65535 || D < 1 || D > 256) return DIB_BAD_SIZE;
+  if (form == 1) {
+    if (D <= 64) return launch_recurrence_wide<4, 8>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+    if (D <= 128) return launch_recurrence_wide<8, 6>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+    return launch_recurrence_wide<16, 4>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
+  }
   if (D <= 64) return launch_recurrence<16, 8>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
   if (D <= 128) return launch_recurrence<32, 6>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);
   return launch_recurrence<64, 4>(packed, state, o_out, cu_q_lens, state_slots, B, H, D, st);

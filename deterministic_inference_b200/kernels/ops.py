@@ -903,6 +903,24 @@ def sigmoid_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: floa
 
 # ---------------------------------------------------------------- generalised delta rule
 
+# DIB200_DELTA_FORM (read once): 0 / 1 force a form of the recurrence kernel for every sequence
+DELTA_FORM = __import__("os").environ.get("DIB200_DELTA_FORM", "auto")
+
+
+def delta_rule_forms(step) -> list:
+    """[(form, first sequence, sequences)] of the recurrence's launches: the step's leading
+    one-token sequences (decoded tokens) run on form 0 (a column's rows over 4 lanes: the state
+    is read and written once, with the fewest CTAs), the sequences that bring prompt portions on
+    form 1 (rows over 16 lanes, a quarter of the instructions per token and warp).  The forms
+    order a sum's terms differently, so which one a sequence runs on depends on what IT brings,
+    not on the rest of the batch."""
+    n = step.num_seqs
+    if DELTA_FORM in ("0", "1"):
+        return [(int(DELTA_FORM), 0, n)]
+    nd = min(int(getattr(step, "num_decode", 0) or 0), n)
+    return [(f, a, m) for f, a, m in ((0, 0, nd), (1, nd, n - nd)) if m > 0]
+
+
 def delta_rule(proj, w2_t: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: torch.Tensor,
                state: torch.Tensor, step, num_heads: int, head_dim: int, lora_rank: int,
                decay_scale: float, key_eps: float, norm_eps: float, out_dtype) -> torch.Tensor:
@@ -935,10 +953,12 @@ def delta_rule(proj, w2_t: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: 
                                c_float(decay_scale), c_float(key_eps), _stream())
     _check(st, "delta_rule(prepare)", f"heads {num_heads} of {head_dim}, rank {lora_rank}")
     o = torch.empty(t, num_heads, head_dim, dtype=torch.float32, device=dev)
-    st = lib.dib_delta_recurrence(_ptr(packed), _ptr(state), _ptr(o), _ptr(step.cu_q_lens),
-                                  _ptr(step.state_slots), c_int(step.num_seqs), c_int(num_heads),
-                                  c_int(head_dim), _stream())
-    _check(st, "delta_rule(recurrence)", f"heads of {head_dim} (at most 256)")
+    for form, first, count in delta_rule_forms(step):
+        st = lib.dib_delta_recurrence(_ptr(packed), _ptr(state), _ptr(o),
+                                      c_void_p(step.cu_q_lens.data_ptr() + 4 * first),
+                                      c_void_p(step.state_slots.data_ptr() + 4 * first), c_int(count),
+                                      c_int(num_heads), c_int(head_dim), c_int(form), _stream())
+        _check(st, "delta_rule(recurrence)", f"heads of {head_dim} (at most 256)")
     out = torch.empty(t, hd, dtype=out_dtype, device=dev)
     st = lib.dib_delta_output(_ptr(o), *src, _ptr(norm_weight), _ptr(out), c_int(_DT[out_dtype]), c_int(t),
                               c_int(num_heads), c_int(head_dim), c_int(lora_rank), c_float(norm_eps), _stream())

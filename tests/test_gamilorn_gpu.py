@@ -217,9 +217,12 @@ def test_delta_rule_alone(dtype, heads, dim, rank):
         cu = [0]
         for c in counts:
             cu.append(cu[-1] + c)
+        lead = 0                       # the step's leading one-token sequences: the kernel form of decoded tokens
+        while lead < len(counts) and counts[lead] == 1:
+            lead += 1
         step = SimpleNamespace(cu_q_lens=torch.tensor(cu, dtype=torch.int32, device=dev),
                                state_slots=torch.tensor([slot_of[s] for s in who], dtype=torch.int32, device=dev),
-                               num_seqs=len(who))
+                               num_seqs=len(who), num_decode=lead)
         y = ops.delta_rule(x.to(dev), w2.to(dt).t().contiguous().to(dev), w0.to(dev), a_bias.to(dev), norm_w.to(dev), state, step,
                            heads, dim, rank, decay_scale, key_eps, eps, dt).cpu().double()
         for j, (s, c) in enumerate(zip(who, counts)):
