@@ -28,9 +28,6 @@ from pathlib import Path
 from ..parts.spec import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
 from .model_config import ConfigError
 
-_DEFAULT_DECAY_RANK = 16
-
-
 def _positive(what: str, v) -> int:
     if not isinstance(v, int) or isinstance(v, bool) or v < 1:
         raise ConfigError(f"{what} must be a positive integer, got {v!r}")
@@ -84,7 +81,10 @@ class GamilornConfig:
                 _positive(f"layer {i}: right.{k}", right.get(k))
             rank = None if decay_ranks is None else decay_ranks[i]
             if rank is None:
-                rank = right.get("decay_rank", _DEFAULT_DECAY_RANK)
+                rank = right.get("decay_rank")
+            if rank is None:
+                raise ConfigError(f"layer {i}: the rank of the decay map is not known: no checkpoint tensor "
+                                  "to read it from and no right.decay_rank")
             right["decay_rank"] = _positive(f"layer {i}: right.decay_rank", int(rank))
             mlp = layer.get("mlp")
             if mlp is not None:

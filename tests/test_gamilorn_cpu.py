@@ -77,6 +77,7 @@ def test_a_preset_and_the_command_line_write_a_model_folder_the_registry_reads_b
     (lambda c: c["layers"][0]["mixer"]["left"]["mask"].__setitem__("size", 0), "mask.size"),
     (lambda c: c["layers"][0]["mlp"].__setitem__("kind", "experts"), "mlp.kind"),
     (lambda c: c.__setitem__("layers", []), "no layers"),
+    (lambda c: c["layers"][1]["mixer"]["right"].pop("decay_rank"), "rank of the decay map"),
 ])
 def test_a_configuration_that_cannot_run_is_refused_with_the_reason(edit, text):
     cfg = copy.deepcopy(gu.CONFIGS["g1"]["config"])
