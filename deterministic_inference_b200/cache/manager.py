@@ -107,10 +107,10 @@ class PageGroup:
 
     def release_passed(self, slot: int, next_position: int) -> int:
         """Window groups: give back pages all of whose positions are older than
-        the window of a query at ``next_position``.  Returns how many."""
+        the window (or lie before the chunk) of a query at ``next_position``.  Returns how many."""
         if self.window is None:
             return 0
-        first_needed = next_position - self.window + 1
+        first_needed = self.spec.first_needed(next_position)
         n = 0
         pl = self.pages[slot]
         kept = -(-self.keep_first // self.page_size)     # pages that hold a kept position

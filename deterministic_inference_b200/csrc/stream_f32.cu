@@ -18,6 +18,65 @@ __global__ void embed_pos_kernel(const void* table, const void* pos_table, int d
         __fadd_rn(load_as(table, dtype, (long long)id * W + c), load_as(pos_table, dtype, (long long)p * W + c));
 }
 
+// out[t] = table[ids[t]] * scale, float32
+__global__ void embed_scale_kernel(const void* table, int dtype, const int* ids, float scale, float* out,
+                                   int T, int W, int V) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  for (int c = threadIdx.x; c < W; c += blockDim.x)
+    out[(long long)t * W + c] = __fmul_rn(load_as(table, dtype, (long long)id * W + c), scale);
+}
+
+// One block per row: residual[row] += x[row] / sqrt(mean(x[row]^2) + eps_x) * wx (+ bias), the
+// normed output of the part before added to the stream without being rounded; then, when out is
+// given, out[row] = residual[row] / sqrt(mean(residual[row]^2) + eps) * w.  x null: only the bias
+// is added.
+__global__ void stream_normed_add_kernel(float* residual, Source x, const float* wx, float eps_x,
+                                         const float* bias, const float* w, void* out, int out_dtype,
+                                         int W, float eps) {
+  __shared__ float scratch[32];
+  pdl_prologue(x.p);
+  const long long base = (long long)blockIdx.x * W;
+  float rx = 0.f;
+  if (x.p != nullptr) {
+    float sx = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float v = source_load(x, base + c);
+      sx = __fmaf_rn(v, v, sx);
+    }
+    rx = 1.0f / sqrtf(block_sum(sx, scratch) / (float)W + eps_x);
+  }
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float r = residual[base + c];
+    if (x.p != nullptr) r = __fadd_rn(r, source_load(x, base + c) * rx * wx[c]);
+    if (bias != nullptr) r = __fadd_rn(r, bias[c]);
+    residual[base + c] = r;
+    ss = __fmaf_rn(r, r, ss);
+  }
+  if (out == nullptr) return;
+  const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x)
+    store_as(out, out_dtype, base + c, residual[base + c] * rstd * w[c]);
+}
+
+// [gate | up] rows of width 2I -> I: g = min(gate, limit), u = clamp(up, -limit, limit),
+// y = g * sigmoid(alpha * g) * (u + 1)
+__global__ void limited_gate_kernel(Source gu, float limit, float alpha, void* out, int out_dtype,
+                                    int rows, int I) {
+  pdl_prologue(gu.p);
+  const long long n = (long long)rows * I;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / I, c = i % I;
+    const float g = fminf(source_load(gu, r * 2 * I + c), limit);
+    const float u = fminf(fmaxf(source_load(gu, r * 2 * I + I + c), -limit), limit);
+    store_as(out, out_dtype, i, g * sigmoid_f32(alpha * g) * (u + 1.0f));
+  }
+}
+
 // One block per row.  TERMS > 0: residual[row] += a0 * x0[row] (+ a1 * x1[row]) first, the
 // terms added in their order; then out[row] = residual[row] / sqrt(mean(residual[row]^2) + eps)
 // * w.  The sum of squares is taken by a block of a width that depends on W alone.
@@ -88,6 +147,42 @@ int dib_embed_pos(const void* table, const void* pos_table, int dtype, const int
   if (W < 1 || V < 1 || P < 1) return DIB_BAD_SIZE;
   dib_launch(embed_pos_kernel, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, st, table, pos_table, dtype, ids,
              positions, out, T, W, V, P);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_embed_scale(const void* table, int dtype, const int* ids, float scale, float* out, int T, int W,
+                    int V, cudaStream_t st) {
+  if (T == 0) return DIB_OK;
+  if (dtype != 0 && dtype != 1) return DIB_BAD_DTYPE;
+  if (W < 1 || V < 1) return DIB_BAD_SIZE;
+  dib_launch(embed_scale_kernel, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, st, table, dtype, ids, scale, out,
+             T, W, V);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// x null: no normed term; bias null: none; out null: the stream is updated and nothing is normed.
+int dib_stream_normed_add(float* residual, const void* x, int kind, int splits, long long stride,
+                          const float* wx, float eps_x, const float* bias, const float* w, void* out,
+                          int out_dtype, int rows, int W, float eps, cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (W < 1) return DIB_BAD_SIZE;
+  if (out != nullptr && out_dtype != 0 && out_dtype != 1) return DIB_BAD_DTYPE;
+  const dim3 grid(rows), block(W >= 2048 ? 512 : (W >= 512 ? 256 : 128));
+  dib_launch(stream_normed_add_kernel, grid, block, 0, st, residual, make_source(x, kind, splits, stride), wx,
+             eps_x, bias, w, out, out_dtype, W, eps);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_limited_gate(const void* gu, int kind, int splits, long long stride, float limit, float alpha,
+                     void* out, int out_dtype, int rows, int I, cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (I < 1) return DIB_BAD_SIZE;
+  if (out_dtype != 0 && out_dtype != 1) return DIB_BAD_DTYPE;
+  dib_launch(limited_gate_kernel, dim3(flat_grid((long long)rows * I, 256)), dim3(256), 0, st,
+             make_source(gu, kind, splits, stride), limit, alpha, out, out_dtype, rows, I);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

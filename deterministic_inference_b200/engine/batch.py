@@ -313,7 +313,7 @@ def check_packed(host: np.ndarray, lay: PackedLayout, cache, group_list: list, v
             need_pages = -(-int(lens[bi]) // g.page_size)
             row = bt[bi, :0]
             if g.window is not None:
-                first_needed = max(0, int(lens[bi]) - int(cu[bi + 1] - cu[bi]) - g.window + 1) // g.page_size
+                first_needed = g.spec.first_needed(int(lens[bi]) - int(cu[bi + 1] - cu[bi])) // g.page_size
                 # the pages of the positions a window keeps readable for good
                 row = bt[bi, :min(-(-g.keep_first // g.page_size), first_needed, need_pages, lay.width)]
             row = np.concatenate([row, bt[bi, first_needed:min(need_pages, lay.width)]])

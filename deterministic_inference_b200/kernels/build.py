@@ -42,6 +42,7 @@ SOURCES = {
     "stream_f32": "stream_f32.cu",
     "sigmoid_attention": "sigmoid_attention.cu",
     "delta_rule": "delta_rule.cu",
+    "masked_attention": "masked_attention.cu",
 }
 HEADERS = ("common.cuh", "attention_merge.cuh")
 # further headers a library includes
@@ -52,6 +53,7 @@ EXTRA_HEADERS = {
     "stream_f32": ("source.cuh",),
     "sigmoid_attention": ("source.cuh", "sigmoid_attention_mma.cuh"),
     "delta_rule": ("source.cuh",),
+    "masked_attention": ("source.cuh", "masked_attention_mma.cuh"),
 }
 
 NVCC_FLAGS = [

@@ -287,7 +287,31 @@ class WeightedSum:
         return out
 
 
-_DEFERRED = (SplitSum, GatedSplit, SplitAttention, WeightedSum)
+class NormedTerm:
+    """x / sqrt(mean(x^2) + eps) * weight that is not computed yet: the output of a part that is
+    normed before it joins a float32 residual stream.  The stream's next norm computes it in float32
+    and adds it to the stream without rounding it (``stream_rms_norm``); ``tensor()`` gives it as a
+    float32 tensor.  ``x``: a tensor or a ``SplitSum``."""
+
+    def __init__(self, x, weight: torch.Tensor, eps: float):
+        self.x, self.weight, self.eps = x, weight, float(eps)
+        self.dtype = torch.float32
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+    def tensor(self) -> torch.Tensor:
+        rows, width = self.shape
+        out = torch.zeros(rows, width, dtype=torch.float32, device=self.device)
+        return stream_add_(out, self)
+
+
+_DEFERRED = (SplitSum, GatedSplit, SplitAttention, WeightedSum, NormedTerm)
 
 
 def _source_args(x):
@@ -568,6 +592,8 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 def gather_rows(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     """out[r] = x[index[r]]; index int32."""
+    if isinstance(x, NormedTerm):          # a norm works row by row: gather first
+        return NormedTerm(gather_rows(x.x, index), x.weight, x.eps)
     x = as_tensor(x)
     _need(x, "x", None, 2)
     _need(index, "index", torch.int32, 1)
@@ -741,6 +767,10 @@ def stream_rms_norm(stream: torch.Tensor, weight: torch.Tensor, eps: float, out_
     rows, w = stream.shape
     if weight.shape[0] != w:
         raise KernelError(f"stream_rms_norm: weight has {weight.shape[0]} elements, rows have {w}")
+    if isinstance(add, NormedTerm):
+        out = torch.empty(rows, w, dtype=out_dtype, device=stream.device)
+        stream_add_(stream, add, norm_weight=weight, norm_eps=eps, out=out)
+        return out
     terms = []
     if add is not None:
         terms = add.terms if isinstance(add, WeightedSum) else [(1.0, add)]
@@ -752,6 +782,58 @@ def stream_rms_norm(stream: torch.Tensor, weight: torch.Tensor, eps: float, out_
                                             _ptr(weight), _ptr(out), c_int(_DT[out_dtype]), c_int(rows),
                                             c_int(w), c_float(eps), _stream())
     _check(st, "stream_rms_norm", f"row width {w}")
+    return out
+
+
+def stream_add_(stream: torch.Tensor, term=None, bias=None, norm_weight=None, norm_eps: float = 0.0,
+                out=None) -> torch.Tensor:
+    """In place, float32: stream += term (a ``NormedTerm``: computed here, never rounded) + bias (a
+    float32 vector added to every row); with ``out`` also out = RMSNorm(stream) * norm_weight.
+    Returns the stream."""
+    _need(stream, "stream", torch.float32, 2)
+    rows, w = stream.shape
+    src, wx, eps_x = (c_void_p(0), c_int(0), c_int(1), c_longlong(0)), None, 0.0
+    if term is not None:
+        if not isinstance(term, NormedTerm) or tuple(term.shape) != (rows, w):
+            raise KernelError(f"stream_add_: a normed term of shape {(rows, w)} is needed")
+        _need(term.weight, "term.weight", torch.float32, 1)
+        src, wx, eps_x = _source_args(term.x), term.weight, term.eps
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != w:
+            raise KernelError(f"stream_add_: bias has {bias.shape[0]} elements, rows have {w}")
+    if out is not None:
+        _need(norm_weight, "norm_weight", torch.float32, 1)
+        _need(out, "out", None, 2)
+    st = _lib("stream_f32").dib_stream_normed_add(
+        _ptr(stream), *src, _ptr(wx), c_float(eps_x), _ptr(bias), _ptr(norm_weight), _ptr(out),
+        c_int(_DT[out.dtype] if out is not None else 0), c_int(rows), c_int(w), c_float(norm_eps), _stream())
+    _check(st, "stream_add_", f"row width {w}")
+    return stream
+
+
+def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+    """float32 [T, W]: table[ids[t]] * scale."""
+    _need(ids, "ids", torch.int32, 1)
+    _need(table, "table", None, 2)
+    out = torch.empty(ids.shape[0], table.shape[1], dtype=torch.float32, device=table.device)
+    st = _lib("stream_f32").dib_embed_scale(_ptr(table), c_int(_dt(table, "table")), _ptr(ids), c_float(scale),
+                                            _ptr(out), c_int(ids.shape[0]), c_int(table.shape[1]),
+                                            c_int(table.shape[0]), _stream())
+    _check(st, "embedding_scaled")
+    return out
+
+
+def limited_gate(gate_up, limit: float, alpha: float, out_dtype) -> torch.Tensor:
+    """[T, 2I] = [gate | up] -> [T, I]: g = min(gate, limit), u = clamp(up, -limit, limit),
+    g * sigmoid(alpha * g) * (u + 1); float32 arithmetic on the product's accumulator where it is at hand."""
+    rows, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError(f"limited_gate: width {two_i} is odd")
+    out = torch.empty(rows, two_i // 2, dtype=out_dtype, device=gate_up.device)
+    st = _lib("stream_f32").dib_limited_gate(*_source_args(gate_up), c_float(limit), c_float(alpha), _ptr(out),
+                                             c_int(_DT[out_dtype]), c_int(rows), c_int(two_i // 2), _stream())
+    _check(st, "limited_gate")
     return out
 
 
@@ -965,3 +1047,160 @@ def delta_rule(proj, w2_t: torch.Tensor, w0: torch.Tensor, a_bias, norm_weight: 
     _check(st, "delta_rule(output)")
     return out
 
+
+
+# ---------------------------------------------------------------- softmax attention with a mask kind
+
+MASK_KINDS = {"causal": 0, "window": 1, "chunk": 2}
+
+
+def _mask_args(mask: str, size) -> tuple:
+    if mask not in MASK_KINDS:
+        raise KernelError(f"mask {mask!r} is not known: {sorted(MASK_KINDS)}")
+    if mask != "causal" and (size is None or int(size) < 1):
+        raise KernelError(f"a {mask} mask needs a positive size")
+    return MASK_KINDS[mask], int(size) if mask != "causal" else 0
+
+
+def _cache_pages(kv_cache, page_elems: int, what: str) -> int:
+    if kv_cache.numel() % page_elems or kv_cache.shape[0] != kv_cache.numel() // page_elems:
+        raise KernelError(f"{what}: cache of shape {tuple(kv_cache.shape)} is not [pages, ...] of pages of "
+                          f"{page_elems} elements")
+    return kv_cache.shape[0]
+
+
+def attn_prepare(proj, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, q_norm_weight,
+                 k_norm_weight, eps: float, freq, rotary_dim: int, positions: torch.Tensor, kv_cache,
+                 slot_mapping, page_size: int, out_dtype) -> torch.Tensor:
+    """From each token's projection row [q heads | k heads | v heads | anything else]: per-head RMS norm
+    of q and k (when a weight is given), rotation of the first ``rotary_dim`` elements of each head by
+    the token's position (element i with i + rotary_dim / 2, angle = position * freq[i], float32), q
+    [T, Hq, D] returned, k and v to the token's slot of the paged cache (a page: keys [Hkv, page_size,
+    D], then values [Hkv, page_size, Dv])."""
+    t, width = proj.shape
+    need = num_heads * head_dim + num_kv_heads * (head_dim + v_head_dim)
+    if width < need:
+        raise KernelError(f"attn_prepare: rows of {width} elements, q, k and v need {need}")
+    for w, n in ((q_norm_weight, "q_norm_weight"), (k_norm_weight, "k_norm_weight")):
+        if w is not None:
+            _need(w, n, torch.float32, 1)
+            if w.shape[0] != head_dim:
+                raise KernelError(f"{n} has {w.shape[0]} elements, heads have {head_dim}")
+    if freq is not None:
+        _need(freq, "freq", torch.float32, 1)
+        if freq.shape[0] * 2 != rotary_dim:
+            raise KernelError(f"attn_prepare: {freq.shape[0]} frequencies for {rotary_dim} rotated elements")
+    _need(positions, "positions", torch.int32, 1)
+    num_pages = 0
+    if kv_cache is not None:
+        _need(kv_cache, "kv_cache", out_dtype)
+        _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        num_pages = _cache_pages(kv_cache, num_kv_heads * page_size * (head_dim + v_head_dim), "attn_prepare")
+    q = torch.empty(t, num_heads, head_dim, dtype=out_dtype, device=proj.device)
+    st = _lib("masked_attention").dib_attn_prepare(
+        *_source_args(proj), c_longlong(width), _ptr(q), _ptr(kv_cache), _ptr(q_norm_weight), _ptr(k_norm_weight),
+        c_float(eps), _ptr(freq), c_int(rotary_dim if freq is not None else 0), _ptr(positions),
+        _ptr(slot_mapping), c_int(t), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(v_head_dim),
+        c_int(page_size), c_longlong(num_pages), c_int(_DT[out_dtype]), _stream())
+    _check(st, "attn_prepare", f"heads {num_heads}/{num_kv_heads} of {head_dim}/{v_head_dim}")
+    return q
+
+
+def latent_prepare(proj, num_heads: int, plain_dim: int, rot_dim: int, rank: int, latent_norm_weight,
+                   eps: float, freq, positions, kv_cache, slot_mapping, page_size: int, out_dtype) -> torch.Tensor:
+    """From each token's projection row [q: heads of (plain_dim + rot_dim) | latent: rank | rotated key
+    part: rot_dim]: the latent, RMS-normed with its weight, and the rotated key part go to the token's
+    cache row [rank + rot_dim]; the rotated part of every query head goes to q[t, h, rank:], where q
+    [T, H, rank + rot_dim] is returned with its first ``rank`` columns still to be filled (by the
+    product of the head's plain part with its key map)."""
+    t, width = proj.shape
+    if width != num_heads * (plain_dim + rot_dim) + rank + rot_dim:
+        raise KernelError(f"latent_prepare: rows of {width} elements, expected "
+                          f"{num_heads * (plain_dim + rot_dim) + rank + rot_dim}")
+    _need(latent_norm_weight, "latent_norm_weight", torch.float32, 1)
+    _need(freq, "freq", torch.float32, 1)
+    if freq.shape[0] * 2 != rot_dim or latent_norm_weight.shape[0] != rank:
+        raise KernelError("latent_prepare: frequencies or norm weight of the wrong size")
+    _need(positions, "positions", torch.int32, 1)
+    num_pages = 0
+    if kv_cache is not None:
+        _need(kv_cache, "kv_cache", out_dtype)
+        _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        num_pages = _cache_pages(kv_cache, page_size * (rank + rot_dim), "latent_prepare")
+    q = torch.empty(t, num_heads, rank + rot_dim, dtype=out_dtype, device=proj.device)
+    st = _lib("masked_attention").dib_latent_prepare(
+        *_source_args(proj), c_longlong(width), _ptr(q), _ptr(kv_cache), _ptr(latent_norm_weight), c_float(eps),
+        _ptr(freq), _ptr(positions), _ptr(slot_mapping), c_int(t), c_int(num_heads), c_int(plain_dim),
+        c_int(rot_dim), c_int(rank), c_int(page_size), c_longlong(num_pages), c_int(_DT[out_dtype]), _stream())
+    _check(st, "latent_prepare")
+    return q
+
+
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[m, h, n] = sum_k x[m, h, k] * weight[h, k, n]: a product per head.  ``x`` [M, H, K] and
+    ``out`` [M, H, N] may be views with any row and head stride (their last dimension contiguous);
+    ``weight`` [H, K, N] is contiguous.  float32 accumulation, k in ascending order."""
+    _need(weight, "weight", x.dtype, 3)
+    h, k, n = weight.shape
+    for v, name, last in ((x, "x", k), (out, "out", n)):
+        if not v.is_cuda or v.dim() != 3 or v.shape[1] != h or v.shape[2] != last or v.stride(2) != 1 \
+                or v.dtype != x.dtype:
+            raise KernelError(f"heads_linear: {name} of shape {tuple(v.shape)}, stride {v.stride()} against "
+                              f"weight {tuple(weight.shape)}")
+    if out.shape[0] != x.shape[0]:
+        raise KernelError("heads_linear: x and out differ in rows")
+    m = x.shape[0]
+    if x.dtype == torch.bfloat16 and m > HEADS_LINEAR_LIBRARY_ROWS:
+        # many rows: the library's batched product, as for the other products of many rows
+        _launched(2)
+        out.transpose(0, 1).copy_(torch.bmm(x.transpose(0, 1), weight))
+        return out
+    st = _lib("masked_attention").dib_heads_linear(
+        _ptr(x), c_longlong(x.stride(0)), c_longlong(x.stride(1)), _ptr(weight), _ptr(out),
+        c_longlong(out.stride(0)), c_longlong(out.stride(1)), c_int(m), c_int(h), c_int(k), c_int(n),
+        c_int(_dt(x, "x")), _stream())
+    _check(st, "heads_linear", f"M={m} H={h} K={k} N={n}")
+    return out
+
+
+# bfloat16 rows above which ``heads_linear`` is the library's batched product
+HEADS_LINEAR_LIBRARY_ROWS = 64
+
+
+def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float, num_kv_heads: int,
+                     v_head_dim: int, page_size: int, mask: str = "causal", mask_size=None, sink=None,
+                     gate=None, gate_col: int = 0, values_in_keys: bool = False) -> torch.Tensor:
+    """[T, Hq, Dv]: softmax attention of every token of the step over the keys of its sequence in the
+    paged cache that ``mask`` lets it see (a query at position p: "causal" 0 .. p; "window" p - size + 1
+    .. p; "chunk" floor(p / size) * size .. p).  ``sink`` float32 [Hq]: the denominator also holds
+    exp(sink[h]) (no key, no value, not scaled).  ``gate`` [T, >= gate_col + Hq * Dv] (a tensor or split
+    sums): the output is multiplied by sigmoid(gate[t, gate_col + h * Dv + d]).  ``values_in_keys``: the
+    cache holds keys only and a key's first Dv elements are its value."""
+    _need(q, "q", None, 3)
+    _need(kv_cache, "kv_cache", q.dtype)
+    t, hq, dk = q.shape
+    dv_stored = 0 if values_in_keys else v_head_dim
+    if hq % num_kv_heads:
+        raise KernelError(f"masked_attention: {hq} heads over {num_kv_heads} key/value heads")
+    _cache_pages(kv_cache, num_kv_heads * page_size * (dk + dv_stored), "masked_attention")
+    kind, size = _mask_args(mask, mask_size)
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != hq:
+            raise KernelError(f"masked_attention: {sink.shape[0]} sinks for {hq} heads")
+    gate_args, gate_row = (c_void_p(0), c_int(0), c_int(1), c_longlong(0)), 0
+    if gate is not None:
+        if gate.shape[0] != t or gate.shape[1] < gate_col + hq * v_head_dim:
+            raise KernelError(f"masked_attention: gate of shape {tuple(gate.shape)}")
+        gate_args, gate_row = _source_args(gate), gate.shape[1]
+    _need(meta.block_table, "block_table", torch.int32, 2)
+    _need(meta.token_seq, "token_seq", torch.int32, 1)
+    _need(meta.positions, "positions", torch.int32, 1)
+    out = torch.empty(t, hq, v_head_dim, dtype=q.dtype, device=q.device)
+    st = _lib("masked_attention").dib_masked_attention(
+        _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
+        _ptr(meta.token_seq), _ptr(meta.positions), c_int(t), c_int(hq), c_int(num_kv_heads), c_int(dk),
+        c_int(v_head_dim), c_int(dv_stored), c_int(page_size), c_float(scale), c_int(kind), c_int(size),
+        _ptr(sink), *gate_args, c_longlong(gate_row), c_longlong(gate_col), c_int(_dt(q, "q")), _stream())
+    _check(st, "masked_attention", f"heads {hq}/{num_kv_heads}, sizes {dk}/{v_head_dim}")
+    return out

@@ -12,8 +12,8 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, BuildContext, ModelPlan,
-                     TensorSpec)
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, STREAM_ADDENDS, BuildContext,
+                     ModelPlan, TensorSpec)
 
 
 class DecoderModel:
@@ -25,6 +25,7 @@ class DecoderModel:
         self.ctx = BuildContext(dtype=dtype, device=self.device)
         self.blocks = []
         self.mixers = []
+        self.after_layer = None    # a debugging hook: called with (entry, hidden, residual) after every block
         for spec in plan.layers:
             mixer = MIXERS.build(spec.mixer, self.ctx)
             ff = FEED_FORWARDS.build(spec.feed_forward, self.ctx)
@@ -36,6 +37,8 @@ class DecoderModel:
         self.final_norm = NORMS.build(plan.final_norm, self.ctx)
         self.embedding = EMBEDDINGS.build(plan.embedding, self.ctx)
         self.head = HEADS.build(plan.head, self.ctx)
+        self.stream_addend = None if plan.stream_addend is None \
+            else STREAM_ADDENDS.build(plan.stream_addend, self.ctx)
 
     # ---- weights ------------------------------------------------------------
 
@@ -46,6 +49,9 @@ class DecoderModel:
             yield b.feed_forward
             yield b.mixer_norm
             yield b.feed_forward_norm
+            yield from getattr(b, "extra_parts", ())
+        if self.stream_addend is not None:
+            yield self.stream_addend
         yield self.final_norm
         yield self.head
 
@@ -113,8 +119,17 @@ class DecoderModel:
             hidden = self.embedding.forward(step.input_ids)
         residual = None
         for e in self.plan.schedule:
+            if e.enter_vector is not None:
+                # (float32 additions: whether the vector or the pending output joins the stream first
+                # is a matter of rounding alone)
+                if residual is None:
+                    hidden = self.stream_addend.forward(hidden, e.enter_vector)
+                else:
+                    residual = self.stream_addend.forward(residual, e.enter_vector)
             cache = cache_manager.view(e.cache, step, writes=e.writes_cache)
             hidden, residual = self.blocks[e.layer].forward(hidden, residual, step, cache)
+            if self.after_layer is not None:
+                self.after_layer(e, hidden, residual)
         # the head is applied to the requested rows only: gather first, then the
         # last residual add and the final norm on those rows
         if step.num_logits == 0:

@@ -17,6 +17,7 @@ import torch
 
 from ..config.gamilorn_config import GamilornConfig
 from ..config.model_config import Qwen3Config
+from ..config.zatirax_config import ZatiraxConfig
 from .decoder import DecoderModel
 
 
@@ -33,6 +34,7 @@ def register_architecture(name: str, config_class: type) -> None:
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
 register_architecture("Gamilorn", GamilornConfig)
+register_architecture("Zatirax", ZatiraxConfig)
 
 
 def config_from_dir(model_dir):

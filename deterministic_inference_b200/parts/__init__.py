@@ -3,9 +3,9 @@ encodings and block arrangements, each registered under a kind and built from a
 ``PartSpec`` of sizes and constants."""
 
 from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
-                       BuildContext, register_block, register_embedding, register_feed_forward,
+                       STREAM_ADDENDS, BuildContext, register_stream_addend, register_block, register_embedding, register_feed_forward,
                        register_head, register_mixer, register_norm, register_position_encoding)
 from .spec import (CompositeSpec, LayerSpec, ModelPlan, PagedKVSpec, PartSpec, ScheduleEntry, StateSpec,
                    TensorSpec)
-from . import (attention, block, delta_rule, embedding, feed_forward, norm, parallel, position,
-               sigmoid_attention)  # noqa: F401  (register the kinds)
+from . import (attention, block, delta_rule, embedding, feed_forward, latent_attention, masked_attention, norm,
+               parallel, position, sigmoid_attention)  # noqa: F401  (register the kinds)

@@ -8,7 +8,8 @@ later one adds the previous part's output to the residual and norms the sum
 from __future__ import annotations
 
 from .base import Block
-from .registry import register_block
+from .registry import NORMS, register_block
+from .spec import PartSpec
 
 
 @register_block("pre_norm")
@@ -52,4 +53,36 @@ class PreNormStreamBlock(Block):
             return hidden, residual
         hidden, residual = self.feed_forward_norm.add_forward(hidden, residual)
         hidden = self.feed_forward.forward(hidden)
+        return hidden, residual
+
+
+@register_block("sandwich_f32_stream")
+class SandwichStreamBlock(Block):
+    """A norm in front of and behind each sublayer, the residual stream in float32:
+    x <- x + post1(mixer(pre1(x))), then x <- x + post2(feed_forward(pre2(x))).  The post norms are
+    ``stream_post_norm`` parts given as parameters; what they return is added to the stream inside the
+    next norm's kernel (this layer's second norm, the next layer's first, or the model's last), so the
+    block hands its last sublayer's normed output on as the pending term.  A layer without a
+    feed-forward (kind "none") hands on its mixer's."""
+
+    def __init__(self, ctx, mixer, feed_forward, mixer_norm, feed_forward_norm, mixer_post_norm: PartSpec,
+                 feed_forward_post_norm: PartSpec):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.mixer_post_norm = NORMS.build(mixer_post_norm, ctx)
+        self.feed_forward_post_norm = NORMS.build(feed_forward_post_norm, ctx)
+        # parts of this block beyond the four every block has (the model loads their tensors)
+        self.extra_parts = (self.mixer_post_norm, self.feed_forward_post_norm)
+
+    def forward(self, hidden, residual, step, cache):
+        if residual is None:
+            residual = hidden
+            hidden = self.mixer_norm.forward(residual)
+        else:
+            hidden, residual = self.mixer_norm.add_forward(hidden, residual)
+        hidden = self.mixer_post_norm.forward(self.mixer.forward(hidden, step, cache))
+        if self.feed_forward.kind == "none":
+            return hidden, residual
+        hidden, residual = self.feed_forward_norm.add_forward(hidden, residual)
+        hidden = self.feed_forward_post_norm.forward(self.feed_forward.forward(hidden))
         return hidden, residual

@@ -10,8 +10,8 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import Head, TokenEmbedding
-from .registry import register_embedding, register_head
+from .base import Head, Part, TokenEmbedding
+from .registry import register_embedding, register_head, register_stream_addend
 from .spec import TensorSpec
 
 
@@ -61,6 +61,50 @@ class TokenPositionEmbedding(TokenEmbedding):
 
     def forward(self, ids, positions=None):
         return ops.embedding_positions(ids, positions, self.weight, self.positions)
+
+
+@register_embedding("scaled_token_embedding")
+class ScaledTokenEmbedding(TokenEmbedding):
+    """x = table[token] * scale, in float32: this embedding opens a residual stream that is kept
+    in float32."""
+
+    def __init__(self, ctx, name: str, vocab_size: int, hidden_size: int, scale: float):
+        self.name, self.vocab_size, self.hidden_size = name, int(vocab_size), int(hidden_size)
+        self.scale = float(scale)
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.vocab_size, self.hidden_size), role="table")]
+
+    def load(self, tensors):
+        self.weight = tensors[self.name]
+
+    def table(self):
+        return self.weight
+
+    def forward(self, ids):
+        return ops.embedding_scaled(ids, self.weight, self.scale)
+
+
+@register_stream_addend("row_vectors")
+class RowVectors(Part):
+    """``count`` learned vectors of the stream's width; ``forward(stream, i)`` adds vector i to every
+    row of the float32 stream, in place."""
+
+    def __init__(self, ctx, name: str, count: int, hidden_size: int):
+        self.name, self.count, self.hidden_size = name, int(count), int(hidden_size)
+        self.vectors = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.count, self.hidden_size), role="vector", init="normal")]
+
+    def load(self, tensors):
+        self.vectors = tensors[self.name]
+
+    def forward(self, stream, index: int):
+        if not 0 <= index < self.count:
+            raise IndexError(f"{self.name}: vector {index} of {self.count}")
+        return ops.stream_add_(stream, bias=self.vectors[index])
 
 
 @register_head("linear_head")

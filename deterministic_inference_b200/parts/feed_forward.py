@@ -14,27 +14,40 @@ from .spec import TensorSpec
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
+    """``activation`` "silu": silu(gate) * up.  "limited_swish": with g = min(gate, limit) and
+    u = clamp(up, -limit, limit), g * sigmoid(alpha * g) * (u + 1), in float32 from the product's
+    accumulator where it is at hand.  ``names``: the checkpoint names of gate, up and down after the
+    prefix."""
+
     def __init__(self, ctx, prefix: str, hidden_size: int, intermediate_size: int,
-                 activation: str = "silu"):
-        if activation != "silu":
-            raise ValueError(f"gated_mlp: activation {activation!r} has no kernel (only 'silu')")
-        self.prefix = prefix
+                 activation: str = "silu", limit: float = None, alpha: float = 1.702, names=None):
+        if activation not in ("silu", "limited_swish"):
+            raise ValueError(f"gated_mlp: activation {activation!r} has no kernel ('silu', 'limited_swish')")
+        if activation == "limited_swish" and (limit is None or float(limit) <= 0):
+            raise ValueError("gated_mlp: 'limited_swish' needs a positive limit")
+        self.prefix, self.activation = prefix, activation
+        self.limit, self.alpha = None if limit is None else float(limit), float(alpha)
+        self.names = tuple(names) if names else ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.out_dtype = ctx.dtype
         self.w_gate_up = self.w_down = None
 
     def tensor_specs(self):
         p, h, i = self.prefix, self.hidden_size, self.intermediate_size
-        return [TensorSpec(p + "gate_proj.weight", (i, h)), TensorSpec(p + "up_proj.weight", (i, h)),
-                TensorSpec(p + "down_proj.weight", (h, i))]
+        gate, up, down = self.names
+        return [TensorSpec(p + gate, (i, h)), TensorSpec(p + up, (i, h)), TensorSpec(p + down, (h, i))]
 
     def load(self, tensors):
         p = self.prefix
-        self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]],
-                                   dim=0).contiguous()
-        self.w_down = tensors[p + "down_proj.weight"]
+        gate, up, down = self.names
+        self.w_gate_up = torch.cat([tensors[p + gate], tensors[p + up]], dim=0).contiguous()
+        self.w_down = tensors[p + down]
 
     def forward(self, x):
-        return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down)
+        if self.activation == "silu":
+            return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down)
+        gate_up = ops.linear(x, self.w_gate_up, out_dtype=torch.float32 if x.dtype != torch.float32 else None)
+        return ops.linear(ops.limited_gate(gate_up, self.limit, self.alpha, self.out_dtype), self.w_down)
 
 
 @register_feed_forward("dense_mlp")

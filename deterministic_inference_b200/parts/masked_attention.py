@@ -1,0 +1,101 @@
+"""Grouped-query softmax attention over a paged cache, with everything that differs between
+designs as a parameter.
+
+One product of the concatenated weights gives [q | k | v | gate]; query head h reads key/value head
+h // (heads / kv_heads); key heads have ``head_dim`` elements, value heads ``v_head_dim``.
+Optional per-head RMS norm of q and k (one weight of size head_dim each, shared by the heads), then
+the position encoding's rotation of the first ``rotary_dim`` elements of every q and k head (the
+rest pass).  score = q . k * scale.  ``mask``: "causal" (every key up to the query), "window" (the
+last ``mask_size`` keys, the query's own included) or "chunk" (the keys of the query's own chunk of
+``mask_size`` positions, chunks counted from position 0).  ``sink``: the softmax's denominator also
+holds exp(s_h), a learned number per head with no key and no value.  ``gate``: the concatenated
+heads are multiplied by sigmoid(W_g x) before the output projection.  Norms, angles, scores and the
+softmax are float32.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .base import Mixer
+from .registry import POSITION_ENCODINGS, register_mixer
+from .spec import PagedKVSpec, PartSpec, TensorSpec
+
+
+@register_mixer("masked_attention")
+class MaskedAttention(Mixer):
+    def __init__(self, ctx, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 v_head_dim: int, scale: float, position_encoding: Optional[PartSpec] = None,
+                 qk_norm_eps: Optional[float] = None, mask: str = "causal", mask_size: Optional[int] = None,
+                 sink: bool = False, gate: bool = False, names: Optional[dict] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if mask not in ("causal", "window", "chunk"):
+            raise ValueError(f"mask {mask!r} is not known ('causal', 'window', 'chunk')")
+        if mask != "causal" and (mask_size is None or int(mask_size) < 1):
+            raise ValueError(f"a {mask} mask needs a positive mask_size")
+        self.prefix = prefix
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
+        self.scale = float(scale)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.mask, self.mask_size = mask, None if mask == "causal" else int(mask_size)
+        self.sink, self.gate = bool(sink), bool(gate)
+        # checkpoint names of the part's tensors, after the prefix
+        self.names = dict(q="q", k="k", v="v", o="o", gate="g", q_norm="q.norm", k_norm="k.norm", sink="sink")
+        self.names.update(names or {})
+        self.position_encoding = None if position_encoding is None \
+            else POSITION_ENCODINGS.build(position_encoding, ctx)
+        self.rotary_dim = getattr(self.position_encoding, "rotary_dim", 0)
+        self.out_dtype = ctx.dtype
+        self.w_in = self.w_o = self.q_norm = self.k_norm = self.sinks = self.freq = None
+
+    def _sizes(self) -> dict:
+        return dict(q=self.num_heads * self.head_dim, k=self.num_kv_heads * self.head_dim,
+                    v=self.num_kv_heads * self.v_head_dim, gate=self.num_heads * self.v_head_dim)
+
+    def _inputs(self) -> tuple:
+        return ("q", "k", "v", "gate") if self.gate else ("q", "k", "v")
+
+    def tensor_specs(self):
+        p, n, w, sizes = self.prefix, self.names, self.hidden_size, self._sizes()
+        specs = [TensorSpec(p + n[x], (sizes[x], w)) for x in self._inputs()]
+        if self.qk_norm_eps is not None:
+            specs += [TensorSpec(p + n["q_norm"], (self.head_dim,), role="vector", init="one_plus_normal"),
+                      TensorSpec(p + n["k_norm"], (self.head_dim,), role="vector", init="one_plus_normal")]
+        if self.sink:
+            specs.append(TensorSpec(p + n["sink"], (self.num_heads,), role="vector", init="normal"))
+        specs.append(TensorSpec(p + n["o"], (w, self.num_heads * self.v_head_dim)))
+        return specs
+
+    def load(self, tensors):
+        p, n = self.prefix, self.names
+        self.w_in = torch.cat([tensors[p + n[x]] for x in self._inputs()], dim=0).contiguous()
+        self.w_o = tensors[p + n["o"]]
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors[p + n["q_norm"]], tensors[p + n["k_norm"]]
+        if self.sink:
+            self.sinks = tensors[p + n["sink"]]
+        if self.position_encoding is not None and self.rotary_dim:
+            self.freq = self.position_encoding.frequencies()
+
+    def cache_spec(self):
+        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.mask_size, v_head_dim=self.v_head_dim,
+                           mask="chunk" if self.mask == "chunk" else "window")
+
+    def forward(self, x, step, cache):
+        # the projection's float32 accumulator is what the norm, the rotation and the gate read
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32 if x.dtype != torch.float32 else None)
+        q = ops.attn_prepare(proj, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim,
+                             self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.freq, self.rotary_dim,
+                             step.positions, cache.kv if cache.writes else None, cache.slot_mapping,
+                             cache.page_size, self.out_dtype)
+        sizes = self._sizes()
+        o = ops.masked_attention(q, cache.kv, cache.attention_meta, self.scale, self.num_kv_heads,
+                                 self.v_head_dim, cache.page_size, self.mask, self.mask_size, self.sinks,
+                                 gate=proj if self.gate else None,
+                                 gate_col=sizes["q"] + sizes["k"] + sizes["v"])
+        return ops.linear(o.view(o.shape[0], self.num_heads * self.v_head_dim), self.w_o)

@@ -61,6 +61,28 @@ class StreamRMSNorm(Norm):
         return ops.stream_rms_norm(residual, self.weight, self.eps, self.out_dtype, add=x), residual
 
 
+@register_norm("stream_post_norm")
+class StreamPostNorm(Norm):
+    """RMSNorm of a part's OUTPUT on its way into a float32 residual stream:
+    stream += x / sqrt(mean(x^2) + eps) * w.  ``forward`` only wraps its input (``ops.NormedTerm``);
+    the stream's next norm (or ``ops.stream_add_``) computes it in float32 and adds it unrounded."""
+
+    def __init__(self, ctx, name: str, size: int, eps: float):
+        self.name, self.size, self.eps = name, int(size), float(eps)
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.size,), role="vector", init="one_plus_normal")]
+
+    def load(self, tensors):
+        self.weight = tensors[self.name]
+
+    def forward(self, x):
+        if isinstance(x, ops.SplitSum) or isinstance(x, torch.Tensor):
+            return ops.NormedTerm(x, self.weight, self.eps)
+        return ops.NormedTerm(ops.as_tensor(x), self.weight, self.eps)
+
+
 @register_norm("none")
 class NoNorm(Norm):
     """The norm in front of a part that the layer does not have."""

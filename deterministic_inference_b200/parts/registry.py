@@ -61,6 +61,7 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
+STREAM_ADDENDS = Registry("stream addend")     # what a schedule entry may add to the stream on entry
 
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
@@ -69,3 +70,4 @@ register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
 register_block = BLOCKS.register
+register_stream_addend = STREAM_ADDENDS.register

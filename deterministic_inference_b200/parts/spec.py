@@ -46,6 +46,8 @@ class ScheduleEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    enter_vector: Optional[int] = None   # the plan's ``stream_addend`` adds its vector of this index
+                                         # to the residual stream right before the layer runs
 
 
 @dataclass(frozen=True)
@@ -61,10 +63,13 @@ class ModelPlan:
     eos_token_ids: tuple = ()
     ignored_names: tuple = ()         # checkpoint tensors that may be present and are not used
     ignored_substrings: tuple = ()
+    stream_addend: Optional[PartSpec] = None   # learned vectors that schedule entries add to the stream
 
     def validate(self) -> None:
         writers: dict[int, int] = {}
         for pos, e in enumerate(self.schedule):
+            if e.enter_vector is not None and self.stream_addend is None:
+                raise ValueError(f"schedule entry {pos} adds vector {e.enter_vector}, the plan has no stream addend")
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule entry {pos} names layer {e.layer}, "
                                  f"the plan has {len(self.layers)}")
@@ -103,22 +108,45 @@ class TensorSpec:
 class PagedKVSpec:
     """Cache need of an attention-like mixer: keys and values per token.
     ``window`` None: all keys are kept; an int: only the last ``window`` keys are
-    ever read, so older pages can be given back."""
+    ever read, so older pages can be given back.  ``mask`` says what the int means:
+    "window": a query at position p reads the keys p - window + 1 .. p; "chunk": the keys of
+    its own chunk of ``window`` positions, floor(p / window) * window .. p (chunks counted from
+    position 0)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
-    v_head_dim: Optional[int] = None   # size of a value head; None: that of a key head
+    v_head_dim: Optional[int] = None   # size of a value head; None: that of a key head; 0: no
+                                       # values are stored (the mixer reads them out of the keys)
     keep_first: int = 0                # with a window: the first ``keep_first`` keys stay readable
+    mask: str = "window"
+
+    def __post_init__(self):
+        if self.mask not in ("window", "chunk"):
+            raise ValueError(f"mask {self.mask!r} is not known ('window' or 'chunk')")
+        if self.mask == "chunk" and (self.window is None or self.keep_first):
+            raise ValueError("a chunk mask needs a size and keeps no first keys")
 
     @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
+    def first_needed(self, position: int) -> int:
+        """The oldest key a query at ``position`` (or any later one) can read, the kept first
+        keys aside."""
+        if self.window is None:
+            return 0
+        if self.mask == "chunk":
+            return position // self.window * self.window
+        return max(0, position - self.window + 1)
+
     def group_key(self) -> tuple:
         key = ("paged_kv", self.num_kv_heads, self.head_dim, self.window)
-        if self.value_dim != self.head_dim or (self.window is not None and self.keep_first):
+        if self.value_dim != self.head_dim or (self.window is not None and self.keep_first) \
+                or self.mask != "window":
             key += (self.value_dim, self.keep_first if self.window is not None else 0)
+        if self.mask != "window":
+            key += (self.mask,)
         return key
 
 

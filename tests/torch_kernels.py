@@ -129,6 +129,8 @@ def gated_linear(x, w_gate_up):
 
 def gather_rows(x, index):
     """sid/model/qwen3.py:113"""
+    if hasattr(x, "eps") and hasattr(x, "weight"):       # a norm works row by row: gather first
+        return type(x)(gather_rows(x.x, index), x.weight, x.eps)
     if hasattr(x, "terms"):
         x = _plain(x)
     return x[index.long()].contiguous()
@@ -196,6 +198,13 @@ def gumbel_sample(logits, temperatures, seeds, sample_positions, keep=None, top_
 
 def _plain(x):
     """A float32 tensor of a weighted sum that is not added up yet, or of a tensor."""
+    if hasattr(x, "eps") and hasattr(x, "weight"):       # a part's output under its post norm
+        return _rms(_plain(x.x), x.weight, x.eps)
+    if hasattr(x, "parts"):                               # split-k partial products
+        total = x.parts[0].float().clone()
+        for i in range(1, x.parts.shape[0]):
+            total += x.parts[i].float()
+        return total
     if hasattr(x, "terms"):
         total = None
         for a, t in x.terms:
@@ -301,6 +310,121 @@ def delta_rule(proj, w2_t, w0, a_bias, norm_weight, state, step, num_heads, head
     return (o.reshape(t, hd) * norm_weight * torch.sigmoid(g.reshape(t, hd))).to(out_dtype)
 
 
-ALL = ("embedding_positions", "stream_rms_norm", "xielu", "softcap_", "qkv_bias_cache", "sigmoid_attention",
+# ---- softmax attention with a mask kind, latent rows, the float32 stream's other kernels
+
+def embedding_scaled(ids, table, scale):
+    return table[ids.long()].float() * scale
+
+
+def stream_add_(stream, term=None, bias=None, norm_weight=None, norm_eps=0.0, out=None):
+    if term is not None:
+        stream += _plain(term)
+    if bias is not None:
+        stream += bias
+    if out is not None:
+        out.copy_(_rms(stream, norm_weight, norm_eps).to(out.dtype))
+    return stream
+
+
+def limited_gate(gate_up, limit, alpha, out_dtype):
+    x = _plain(gate_up)
+    i = x.shape[1] // 2
+    g, u = torch.clamp(x[:, :i], max=limit), torch.clamp(x[:, i:], -limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out_dtype)
+
+
+def _rotate_first(x, positions, freq, rot):
+    """x [T, heads, D] float32: elements i and i + rot / 2 (i < rot / 2) turned by position * freq[i]."""
+    if freq is None or rot == 0:
+        return x
+    half = rot // 2
+    a = positions[:x.shape[0]].float()[:, None] * freq[None, :]
+    c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
+    u, v = x[..., :half], x[..., half:rot]
+    return torch.cat([u * c - v * s, v * c + u * s, x[..., rot:]], dim=-1)
+
+
+def attn_prepare(proj, num_heads, num_kv_heads, head_dim, v_head_dim, q_norm_weight, k_norm_weight, eps, freq,
+                 rotary_dim, positions, kv_cache, slot_mapping, page_size, out_dtype):
+    x = _plain(proj).to(out_dtype).float()
+    t = x.shape[0]
+    nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * v_head_dim
+    q = x[:, :nq].reshape(t, num_heads, head_dim)
+    k = x[:, nq:nq + nk].reshape(t, num_kv_heads, head_dim)
+    v = x[:, nq + nk:nq + nk + nv].reshape(t, num_kv_heads, v_head_dim)
+    if q_norm_weight is not None:
+        q, k = _rms(q, q_norm_weight, eps), _rms(k, k_norm_weight, eps)
+    q, k = _rotate_first(q, positions, freq, rotary_dim), _rotate_first(k, positions, freq, rotary_dim)
+    if kv_cache is not None:
+        flat = kv_cache.view(kv_cache.shape[0], -1)
+        v_base = num_kv_heads * page_size * head_dim
+        for i, slot in enumerate(slot_mapping.tolist()[:t]):
+            if slot < 0:
+                continue
+            page, off = divmod(slot, page_size)
+            for g in range(num_kv_heads):
+                a = (g * page_size + off) * head_dim
+                flat[page, a:a + head_dim] = k[i, g].to(out_dtype)
+                a = v_base + (g * page_size + off) * v_head_dim
+                flat[page, a:a + v_head_dim] = v[i, g].to(out_dtype)
+    return q.to(out_dtype)
+
+
+def latent_prepare(proj, num_heads, plain_dim, rot_dim, rank, latent_norm_weight, eps, freq, positions, kv_cache,
+                   slot_mapping, page_size, out_dtype):
+    x = _plain(proj).to(out_dtype).float()
+    t = x.shape[0]
+    nq = num_heads * (plain_dim + rot_dim)
+    q_rot = x[:, :nq].reshape(t, num_heads, plain_dim + rot_dim)[:, :, plain_dim:]
+    q = torch.zeros(t, num_heads, rank + rot_dim, dtype=out_dtype)
+    q[:, :, rank:] = _rotate_first(q_rot, positions, freq, rot_dim).to(out_dtype)
+    if kv_cache is not None:
+        latent = _rms(x[:, nq:nq + rank], latent_norm_weight, eps)
+        k_rot = _rotate_first(x[:, None, nq + rank:], positions, freq, rot_dim)[:, 0]
+        rows = kv_cache.view(-1, rank + rot_dim)
+        for i, slot in enumerate(slot_mapping.tolist()[:t]):
+            if slot >= 0:
+                rows[slot] = torch.cat([latent[i], k_rot[i]]).to(out_dtype)
+    return q
+
+
+def heads_linear(x, weight, out):
+    out.copy_(torch.einsum("mhk,hkn->mhn", x.float(), weight.float()).to(out.dtype))
+    return out
+
+
+def masked_attention(q, kv_cache, meta, scale, num_kv_heads, v_head_dim, page_size, mask="causal", mask_size=None,
+                     sink=None, gate=None, gate_col=0, values_in_keys=False):
+    t, hq, dk = q.shape
+    flat = kv_cache.view(kv_cache.shape[0], -1)
+    keys_of = flat[:, :num_kv_heads * page_size * dk].view(-1, num_kv_heads, page_size, dk)
+    values_of = None if values_in_keys else \
+        flat[:, num_kv_heads * page_size * dk:].view(-1, num_kv_heads, page_size, v_head_dim)
+    out = torch.zeros(t, hq, v_head_dim, dtype=torch.float32)
+    seqs, positions = meta.token_seq.tolist(), meta.positions.tolist()
+    group = hq // num_kv_heads
+    g_all = None if gate is None else _plain(gate).to(q.dtype).float()
+    for i in range(t):
+        p = positions[i]
+        lo = 0 if mask == "causal" else (max(0, p - mask_size + 1) if mask == "window" else p // mask_size * mask_size)
+        js = torch.arange(lo, p + 1)
+        pages = meta.block_table[seqs[i]][js // page_size].long()
+        for h in range(hq):
+            k = keys_of[pages, h // group, js % page_size].float()
+            v = k[:, :v_head_dim] if values_in_keys else values_of[pages, h // group, js % page_size].float()
+            s = (k @ q[i, h].float()) * scale
+            if sink is not None:
+                s = torch.cat([s, sink[h].float().reshape(1)])
+            w = torch.softmax(s, dim=0)[:js.shape[0]]
+            out[i, h] = w @ v
+    out = out.to(q.dtype)
+    if g_all is not None:
+        cols = g_all[:, gate_col:gate_col + hq * v_head_dim].reshape(t, hq, v_head_dim)
+        out = (out.float() * torch.sigmoid(cols)).to(q.dtype)
+    return out
+
+
+ALL = ("embedding_scaled", "stream_add_", "limited_gate", "attn_prepare", "latent_prepare", "heads_linear",
+       "masked_attention", "embedding_positions", "stream_rms_norm", "xielu", "softcap_", "qkv_bias_cache", "sigmoid_attention",
        "delta_rule", "patch_token_ids", "embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
        "paged_attention", "silu_mul", "gated_linear", "gather_rows", "linear", "argmax", "gumbel_sample")
