@@ -103,7 +103,7 @@ __device__ __forceinline__ void decode_split_compute(
   const int k0 = split * DEC_SPLIT;
   const int warp = tid >> 5, lane = tid & 31;
   const int pos = kv_len - 1;
-  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first_key = first_visible_key(pos, window);
   const int nvalid = min(DEC_SPLIT, kv_len - k0);
   __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(exch);
   float* sM = reinterpret_cast<float*>(exch + 16 * P_STRIDE * 2);   // [4][16]
@@ -311,7 +311,7 @@ decode_attention_stage1_tma_kernel(const __grid_constant__ CUtensorMap map,
   }
   __syncthreads();
   const int pos = kv_len - 1;
-  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first_key = first_visible_key(pos, window);
   if (k0 > pos || k0 + DEC_SPLIT <= first_key) return;
   const int nvalid = min(DEC_SPLIT, kv_len - k0);
   const int valid_pages = (nvalid + page_size - 1) / page_size;
@@ -359,7 +359,7 @@ __device__ __forceinline__ bool decode_next_item(unsigned& idx, unsigned total, 
     const unsigned b = t / max_splits, split = t % max_splits;
     const int kv_len = seq_lens[b];
     const int pos = kv_len - 1;
-    const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_key = first_visible_key(pos, window);
     const int s0 = first_key / DEC_SPLIT, s1 = pos / DEC_SPLIT;
     unsigned base;
     if (kv_len <= 0 || (int)split > s1) base = (b + 1) * max_splits * Hkv;      // next sequence
@@ -596,7 +596,7 @@ template <int D>
 int launch_decode_tma(const void* q, void* out, const void* cache, long long num_pages,
                       const int* bt, int max_blocks, const int* seq_lens, float* part_o,
                       float* part_lse, int num_seqs, int max_splits, int Hq, int Hkv, int page_size,
-                      float scale, int window, int pipelined, cudaStream_t st) {
+                      float scale, int window, int pipelined, cudaStream_t st, const float* sink = nullptr) {
   const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
   if (map == nullptr) return DIB_LAUNCH_FAILED;
   const int sms = sm_count_of_current_device();
@@ -638,7 +638,7 @@ int launch_decode_tma(const void* q, void* out, const void* cache, long long num
     DIB_CHECK_LAUNCH();
   }
   if (out != nullptr) {   // (no output: the caller merges the partial results itself)
-    launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
+    launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st, sink);
     DIB_CHECK_LAUNCH();
   }
   return DIB_OK;
@@ -669,18 +669,28 @@ void dib_attention_bf16_set_merge_wide_from(int n) { merge_wide_from() = n; }
 // Sequences with more than one new token.  q/out are the step's full [T, Hq, D]
 // tensors; tiles name (sequence, first token of the tile among its new tokens), with
 // floor(64 / (Hq/Hkv)) tokens per tile.
+// window > 0: a sliding window; < 0: chunks of -window positions (see first_visible_key).  sink:
+// float32 [Hq] or null: exp(sink[head]) joins the softmax's denominator.
+int dib_extend_attention_bf16_sink(const void* q, void* out, const void* cache, const int* block_table,
+                                   int max_blocks, const int* cu_q_lens, const int* seq_lens,
+                                   const int* tile_seq, const int* tile_start, int num_tiles, int Hq,
+                                   int Hkv, int D, int page_size, float scale, int window,
+                                   const float* sink, cudaStream_t st) {
+  if (num_tiles == 0) return DIB_OK;
+  if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > EXT_M || num_tiles > 65535) return DIB_BAD_SIZE;
+#define CALL(DD)                                                                              \
+  launch_extend<DD>(q, out, cache, block_table, max_blocks, cu_q_lens, seq_lens, tile_seq,   \
+                    tile_start, num_tiles, Hq, Hkv, page_size, scale, window, st, sink)
+  DIB_DISPATCH_D(D, CALL)
+#undef CALL
+}
 int dib_extend_attention_bf16(const void* q, void* out, const void* cache, const int* block_table,
                               int max_blocks, const int* cu_q_lens, const int* seq_lens,
                               const int* tile_seq, const int* tile_start, int num_tiles, int Hq,
                               int Hkv, int D, int page_size, float scale, int window,
                               cudaStream_t st) {
-  if (num_tiles == 0) return DIB_OK;
-  if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > EXT_M || num_tiles > 65535) return DIB_BAD_SIZE;
-#define CALL(DD)                                                                              \
-  launch_extend<DD>(q, out, cache, block_table, max_blocks, cu_q_lens, seq_lens, tile_seq,   \
-                    tile_start, num_tiles, Hq, Hkv, page_size, scale, window, st)
-  DIB_DISPATCH_D(D, CALL)
-#undef CALL
+  return dib_extend_attention_bf16_sink(q, out, cache, block_table, max_blocks, cu_q_lens, seq_lens, tile_seq,
+                                        tile_start, num_tiles, Hq, Hkv, D, page_size, scale, window, nullptr, st);
 }
 
 // Stage 2 alone: out [num_seqs, Hq, D] from the partial results of a call that was made
@@ -699,12 +709,29 @@ int dib_decode_attention_merge(const float* part_o, const float* part_lse, const
 // index).  part_o: float32 [num_seqs, Hq, max_splits, D]; part_lse: [num_seqs, Hq,
 // max_splits]; max_splits >= ceil(longest sequence / 128).  out == nullptr: only the
 // partial results are made (the caller merges them, see dib_decode_attention_merge).
+int dib_decode_attention_bf16_sink(const void* q, void* out, const void* cache, long long num_pages,
+                                   const int* block_table, int max_blocks, const int* seq_lens,
+                                   float* part_o, float* part_lse, int num_seqs, int max_splits, int Hq,
+                                   int Hkv, int D, int page_size, float scale, int window,
+                                   int pipelined, const float* sink, cudaStream_t st);
 int dib_decode_attention_bf16(const void* q, void* out, const void* cache, long long num_pages,
                               const int* block_table, int max_blocks, const int* seq_lens,
                               float* part_o, float* part_lse, int num_seqs, int max_splits, int Hq,
                               int Hkv, int D, int page_size, float scale, int window,
                               int pipelined, cudaStream_t st) {
+  return dib_decode_attention_bf16_sink(q, out, cache, num_pages, block_table, max_blocks, seq_lens, part_o,
+                                        part_lse, num_seqs, max_splits, Hq, Hkv, D, page_size, scale, window,
+                                        pipelined, nullptr, st);
+}
+// The same with a sink (float32 [Hq] or null) that the merge adds to the denominator; out must be given
+// with a sink (the partial results do not carry it).
+int dib_decode_attention_bf16_sink(const void* q, void* out, const void* cache, long long num_pages,
+                                   const int* block_table, int max_blocks, const int* seq_lens,
+                                   float* part_o, float* part_lse, int num_seqs, int max_splits, int Hq,
+                                   int Hkv, int D, int page_size, float scale, int window,
+                                   int pipelined, const float* sink, cudaStream_t st) {
   if (num_seqs == 0) return DIB_OK;
+  if (sink != nullptr && out == nullptr) return DIB_BAD_SIZE;
   if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16 || num_seqs > 65535 || max_splits > 65535 ||
       max_splits < 1)
     return DIB_BAD_SIZE;
@@ -717,14 +744,14 @@ int dib_decode_attention_bf16(const void* q, void* out, const void* cache, long 
     if (D == 128)
       return launch_decode_tma<128>(q, out, cache, num_pages, block_table, max_blocks, seq_lens,
                                     part_o, part_lse, num_seqs, max_splits, Hq, Hkv, page_size, scale,
-                                    window, pipelined, st);
+                                    window, pipelined, st, sink);
     return launch_decode_tma<64>(q, out, cache, num_pages, block_table, max_blocks, seq_lens, part_o,
                                  part_lse, num_seqs, max_splits, Hq, Hkv, page_size, scale, window,
-                                 pipelined, st);
+                                 pipelined, st, sink);
   }
 #define CALL(DD)                                                                                  \
   launch_decode<DD>(q, out, cache, block_table, max_blocks, seq_lens, part_o, part_lse, num_seqs, \
-                    max_splits, Hq, Hkv, page_size, scale, window, st)
+                    max_splits, Hq, Hkv, page_size, scale, window, st, sink)
   DIB_DISPATCH_D(D, CALL)
 #undef CALL
 }

@@ -236,7 +236,8 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
                         const int* __restrict__ block_table, int max_blocks,
                         const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                         const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
-                        int Hq, int Hkv, int page_size, float scale, int window) {
+                        int Hq, int Hkv, int page_size, float scale, int window,
+                        const float* __restrict__ sink) {
   pdl_prologue(q, cache);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -272,7 +273,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
   }
 
   const int first_pos = prefix + tok0, last_pos = prefix + tok0 + ntok - 1;
-  const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  const int first_key = first_visible_key(first_pos, window);
   const int j0 = first_key / EXT_N, j1 = last_pos / EXT_N;
 
   load_kv_tile<D, EXT_THREADS>(sK0, sK0 + TILE_ELEMS, cache, bt, j0 * EXT_N, EXT_N, kv_len, kvh, Hkv,
@@ -295,7 +296,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     const int tl = r / G;
     if (tl < ntok) {
       hi[rr] = prefix + tok0 + tl;
-      lo[rr] = (window > 0 && hi[rr] - window + 1 > 0) ? hi[rr] - window + 1 : 0;
+      lo[rr] = first_visible_key(hi[rr], window);
     } else {
       hi[rr] = -1;  // sees nothing
       lo[rr] = 0;
@@ -337,6 +338,8 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     const int r = warp * 16 + (lane >> 2) + rr * 8;
     const int tl = r / G, g = r % G;
     if (tl >= ntok) continue;
+    // a sink: exp(sink[head]) joins the denominator (no key, no value, not scaled)
+    if (sink != nullptr) lrow[rr] += fast_exp2(sink[kvh * G + g] * LOG2E - mrow[rr]);
     const float inv = 1.0f / lrow[rr];
     const size_t t = (size_t)(q_begin + tok0 + tl);
     __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * D + (lane & 3) * 2;
@@ -368,7 +371,7 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
   const int G = Hq / Hkv;
   const int kv_len = seq_lens[b];
   const int pos = kv_len - 1;
-  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first_key = first_visible_key(pos, window);
   const int k0 = split * DEC_SPLIT;
   if (k0 > pos || k0 + DEC_SPLIT <= first_key) return;  // nothing visible in this split
   const int* bt = block_table + (size_t)b * max_blocks;
@@ -509,7 +512,8 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
                                                const float* __restrict__ part_lse,
                                                const int* __restrict__ seq_lens,
                                                __nv_bfloat16* __restrict__ out, int max_splits,
-                                               int Hq, int D, int window) {
+                                               int Hq, int D, int window,
+                                               const float* __restrict__ sink) {
   pdl_prologue(part_o, part_lse);
   constexpr int CH = MERGE_CH;
   const int b = blockIdx.x, h = blockIdx.y;
@@ -531,6 +535,8 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
   for (int j = 0; j < CH; ++j)
     if (j >= s0 && j <= s1) M = fmaxf(M, lse_r[j]);
   for (int s = max(s0, CH); s <= s1; ++s) M = fmaxf(M, part_lse[row + s]);
+  // a sink: exp(sink[head]) joins the denominator; without one the sum is left as it is (x + 0 = x)
+  const float sink_w = sink != nullptr ? merge_weight(sink[h], M) : 0.f;
   bool first = true;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float total[1] = {0.f}, total_den = 0.f;
@@ -548,7 +554,7 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
       merge_chunk<1>(lse_r, o_r, c, s0, s1, M, acc, den);
       merge_add<1>(c == c0, acc, den, total, total_den);
     }
-    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(total[0], total_den));
+    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(total[0], __fadd_rn(total_den, sink_w)));
     first = false;
   }
 }
@@ -563,7 +569,7 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
                                     const float* __restrict__ part_lse,
                                     const int* __restrict__ seq_lens,
                                     __nv_bfloat16* __restrict__ out, int max_splits, int Hq, int D,
-                                    int window) {
+                                    int window, const float* __restrict__ sink) {
   pdl_prologue(part_o, part_lse);
   constexpr int CH = MERGE_CH;
   __shared__ float s_acc[MERGE_MAX_CHUNKS][128];
@@ -603,6 +609,7 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
   __syncthreads();
   float M = NEG_BIG;
   for (int k = 0; k < groups; ++k) M = fmaxf(M, s_max[k]);
+  const float sink_w = sink != nullptr ? merge_weight(sink[h], M) : 0.f;
 
   for (int c = g; c <= c1; c += MERGE_GROUPS) {
     if (c < c0) continue;
@@ -618,7 +625,7 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
     float acc[1], den;
     merge_chunk<1>(lse_r, o_r, c, s0, s1, M, acc, den);
     if (c0 == c1) {      // one chunk: its sum is the result
-      if (d < D) out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(acc[0], den));
+      if (d < D) out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(acc[0], __fadd_rn(den, sink_w)));
     } else {
       if (d < D) s_acc[c - c0][d] = acc[0];
       if (d == 0) s_den[c - c0] = den;
@@ -632,7 +639,7 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
       total = __fadd_rn(total, s_acc[k][d]);
       total_den = __fadd_rn(total_den, s_den[k]);
     }
-    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(total, total_den));
+    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(total, __fadd_rn(total_den, sink_w)));
   }
 }
 
@@ -647,24 +654,24 @@ static inline int& merge_wide_from() {
 // wide one.
 static inline void launch_decode_merge(const float* part_o, const float* part_lse, const int* seq_lens,
                                        void* out, int num_seqs, int max_splits, int Hq, int D,
-                                       int window, cudaStream_t st) {
+                                       int window, cudaStream_t st, const float* sink = nullptr) {
   const int th = D < 32 ? 32 : (D + 31) / 32 * 32;
   const int chunks = (max_splits + 15) / 16;
   const int wide_from = merge_wide_from();
   if (max_splits >= wide_from && max_splits > MERGE_CH && th <= 128 && chunks <= MERGE_MAX_CHUNKS)
     dib_launch(decode_attention_stage2_wide_kernel, dim3(num_seqs, Hq),
                dim3(th, chunks < MERGE_GROUPS ? chunks : MERGE_GROUPS), 0, st,
-               part_o, part_lse, seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window);
+               part_o, part_lse, seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window, sink);
   else
     dib_launch(decode_attention_stage2_kernel, dim3(num_seqs, Hq), dim3(th), 0, st, part_o, part_lse,
-               seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window);
+               seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window, sink);
 }
 
 template <int D>
 int launch_extend(const void* q, void* out, const void* cache, const int* bt, int max_blocks,
                   const int* cu_q_lens, const int* seq_lens, const int* tile_seq,
                   const int* tile_start, int num_tiles, int Hq, int Hkv, int page_size, float scale,
-                  int window, cudaStream_t st) {
+                  int window, cudaStream_t st, const float* sink = nullptr) {
   const size_t smem = (size_t)(EXT_M + 4 * EXT_N) * (D + PAD) * sizeof(__nv_bfloat16);
   auto kern = extend_attention_kernel<D>;
   static DeviceOnce attr_set;  // once per instantiation and device; never during a stream capture
@@ -678,7 +685,7 @@ int launch_extend(const void* q, void* out, const void* cache, const int* bt, in
   dib_launch(kern, dim3(grid), dim3(EXT_THREADS), smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                         (const __nv_bfloat16*)cache, bt, max_blocks, cu_q_lens,
                                         seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale,
-                                        window);
+                                        window, sink);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -686,7 +693,8 @@ int launch_extend(const void* q, void* out, const void* cache, const int* bt, in
 template <int D>
 int launch_decode(const void* q, void* out, const void* cache, const int* bt, int max_blocks,
                   const int* seq_lens, float* part_o, float* part_lse, int num_seqs, int max_splits,
-                  int Hq, int Hkv, int page_size, float scale, int window, cudaStream_t st) {
+                  int Hq, int Hkv, int page_size, float scale, int window, cudaStream_t st,
+                  const float* sink = nullptr) {
   size_t smem = (size_t)2 * DEC_SPLIT * (D + PAD) * sizeof(__nv_bfloat16) + 16;  // + 2 barriers
   const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
   if (merge > smem) smem = merge;
@@ -704,7 +712,7 @@ int launch_decode(const void* q, void* out, const void* cache, const int* bt, in
                                         page_size, scale, window);
   DIB_CHECK_LAUNCH();
   if (out != nullptr) {
-    launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
+    launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st, sink);
     DIB_CHECK_LAUNCH();
   }
   return DIB_OK;

@@ -18,7 +18,7 @@ constexpr float MERGE_NEG_BIG = -1e30f;
 // max_splits the scratch holds.
 __device__ __forceinline__ void merge_range(int kv_len, int window, int max_splits, int& s0, int& s1) {
   const int pos = kv_len - 1;
-  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first_key = first_visible_key(pos, window);
   s0 = first_key / MERGE_SPLIT;
   s1 = min(pos / MERGE_SPLIT, max_splits - 1);
 }

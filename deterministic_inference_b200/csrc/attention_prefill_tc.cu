@@ -151,7 +151,8 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
                            const int* __restrict__ block_table, int max_blocks,
                            const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                            const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
-                           int Hq, int Hkv, int page_size, float scale, int window) {
+                           int Hq, int Hkv, int page_size, float scale, int window,
+                           const float* __restrict__ sink) {
   if (threadIdx.x == 0) prefetch_tensormap(&map);
   pdl_prologue(q);
   extern __shared__ unsigned char smem_dyn[];
@@ -184,7 +185,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const int first_pos = prefix + tok0, last_pos = prefix + tok0 + ntok - 1;
-  const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  const int first_key = first_visible_key(first_pos, window);
   const int j0 = first_key / TC_N, j1 = last_pos / TC_N;
   const int ntiles = j1 - j0 + 1;
 
@@ -302,7 +303,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
     const int tl = r / G, g = r % G;
     const bool valid = tl < ntok;
     const int hi = valid ? prefix + tok0 + tl : -1;
-    const int lo = (valid && window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+    const int lo = valid ? first_visible_key(hi, window) : 0;
     const float scale_log2 = scale * LOG2E;
     const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
     float m_ref = NEG_BIG, l = 0.f;
@@ -404,7 +405,9 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
     float* sL = reinterpret_cast<float*>(sP);       // free now
     sL[hf * 128 + r] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    const float l_row = sL[r] + sL[128 + r];
+    float l_row = sL[r] + sL[128 + r];
+    // a sink: exp(sink[head]) joins the denominator (no key, no value, not scaled)
+    if (sink != nullptr && valid) l_row += fast_exp2(sink[kvh * G + g] * LOG2E - m_ref);
     if (ok) {
       const float inv = 1.0f / l_row;
       const size_t t = (size_t)(q_begin + tok0 + tl);
@@ -496,7 +499,8 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
                                 const int* __restrict__ tile_start_b, int Hq, int Hkv,
                                 int page_size, float scale, int window,
                                 int chunk_tiles, const int* __restrict__ tile_chunk, int max_chunks,
-                                float* __restrict__ part_o, float* __restrict__ part_ml) {
+                                float* __restrict__ part_o, float* __restrict__ part_ml,
+                                const float* __restrict__ sink) {
   if (threadIdx.x == 0) prefetch_tensormap(&map);
   pdl_prologue(q);
   extern __shared__ unsigned char smem_dyn[];
@@ -542,7 +546,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
     const int t0 = tokx[x];
     ntok[x] = t0 >= 0 ? max(0, min(npt, q_len - t0)) : 0;
     const int first_pos = prefix + t0, last_pos = prefix + t0 + ntok[x] - 1;
-    const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+    const int first_key = first_visible_key(first_pos, window);
     const int f = first_key / TC_N;
     const int l = ntok[x] > 0 ? last_pos / TC_N : -1;     // an empty tile is never active
     whole[x] = chunk_tiles <= 0 || f / chunk_tiles == l / chunk_tiles;
@@ -779,7 +783,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
     const int tl = r / G, g = r % G;
     const bool valid = tl < ntok[x];
     const int hi = valid ? prefix + tokx[x] + tl : -1;
-    const int lo = (valid && window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+    const int lo = valid ? first_visible_key(hi, window) : 0;
     const float scale_log2 = scale * LOG2E;
     const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
     const unsigned tmem_o = tmem + lane_base + 256 + x * 128;
@@ -935,6 +939,8 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         }
         if (valid) *reinterpret_cast<float2*>(part_ml + row * 2) = make_float2(m_ref, l);
       } else if (ok) {
+        // a sink: exp(sink[head]) joins the denominator (a row cut into chunks gets it in the merge)
+        if (sink != nullptr && valid) l += fast_exp2(sink[kvh * G + g] * LOG2E - m_ref);
         const float inv = 1.0f / l;
         const size_t t = (size_t)(q_begin + tokx[x] + tl);
         __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D;
@@ -976,7 +982,7 @@ extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
                               __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q_lens,
                               const int* __restrict__ seq_lens, const int* __restrict__ token_seq,
                               int t_first, int num_tokens, int Hq, int Hkv, int max_chunks,
-                              int chunk_tiles, int window) {
+                              int chunk_tiles, int window, const float* __restrict__ sink) {
   pdl_prologue(part_o, part_ml);
   const int lane = threadIdx.x & 31;
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -990,7 +996,7 @@ extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
   const int tile_tok0 = (t - q_begin) / npt * npt;
   const int first_pos = prefix + tile_tok0;
   const int last_pos = first_pos + min(npt, q_len - tile_tok0) - 1;
-  const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  const int first_key = first_visible_key(first_pos, window);
   const int c0 = first_key / TC_N / chunk_tiles, c1 = last_pos / TC_N / chunk_tiles;
   if (c0 == c1) return;     // finished by the attention kernel itself
   // Lane j first works out head j's (and j+32's, ...) weights of the chunks, all heads'
@@ -1018,6 +1024,7 @@ extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
         w[c] = m[c] <= -1e29f ? 0.f : fast_exp2(m[c] - M);
         L += l[c] * w[c];
       }
+      if (sink != nullptr && hl < Hq) L += fast_exp2(sink[hl] * LOG2E - M);
       inv = 1.0f / L;
     }
     const int nh = min(32, Hq - h0);
@@ -1106,11 +1113,27 @@ int dib_attention_prefill_tc_status_clear() {
 // Sequences with more than one new token; tiles name (sequence, first token of the
 // tile among its new tokens) with 128 / (Hq/Hkv) tokens per tile.  Returns -2 for
 // shapes this kernel does not take (the caller then uses the mma.sync kernel).
+// window > 0: a sliding window; < 0: chunks of -window positions (first_visible_key).  sink: float32
+// [Hq] or null: exp(sink[head]) joins the softmax's denominator.
+int dib_extend_attention_tc_sink(const void* q, void* out, const void* cache, long long num_pages,
+                                 const int* block_table, int max_blocks, const int* cu_q_lens,
+                                 const int* seq_lens, const int* tile_seq, const int* tile_start,
+                                 int num_tiles, int Hq, int Hkv, int D, int page_size, float scale,
+                                 int window, const float* sink, cudaStream_t st);
 int dib_extend_attention_tc(const void* q, void* out, const void* cache, long long num_pages,
                             const int* block_table, int max_blocks, const int* cu_q_lens,
                             const int* seq_lens, const int* tile_seq, const int* tile_start,
                             int num_tiles, int Hq, int Hkv, int D, int page_size, float scale,
                             int window, cudaStream_t st) {
+  return dib_extend_attention_tc_sink(q, out, cache, num_pages, block_table, max_blocks, cu_q_lens, seq_lens,
+                                      tile_seq, tile_start, num_tiles, Hq, Hkv, D, page_size, scale, window,
+                                      nullptr, st);
+}
+int dib_extend_attention_tc_sink(const void* q, void* out, const void* cache, long long num_pages,
+                                 const int* block_table, int max_blocks, const int* cu_q_lens,
+                                 const int* seq_lens, const int* tile_seq, const int* tile_start,
+                                 int num_tiles, int Hq, int Hkv, int D, int page_size, float scale,
+                                 int window, const float* sink, cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
   if (D != TC_D || Hkv < 1 || Hq % Hkv != 0 || TC_M % (Hq / Hkv) != 0 || page_size < 8 ||
       page_size > TC_N || TC_N % page_size != 0 || num_tiles > 65535 ||
@@ -1129,7 +1152,7 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
   }
   dib_launch(extend_attention_tc_kernel, dim3(Hkv, num_tiles), dim3(TC_THREADS), smem, st, *map,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens,
-             seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale, window);
+             seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale, window, sink);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -1145,6 +1168,14 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
 // and part_ml ([T, Hq, max_chunks, 2]) take the partial results, which a second kernel
 // merges for the tokens t_first .. t_first + num_tokens - 1 (the step's prompt tokens;
 // token_seq names their sequences).
+int dib_extend_attention_tc_pair_sink(const void* q, void* out, const void* cache, long long num_pages,
+                                      const int* block_table, int max_blocks, const int* cu_q_lens,
+                                      const int* seq_lens, const int* tile_seq, const int* tile_start,
+                                      const int* tile_start_b, int num_tiles, int Hq, int Hkv, int D,
+                                      int page_size, float scale, int window, int chunk_tiles,
+                                      const int* tile_chunk, int max_chunks, float* part_o, float* part_ml,
+                                      const int* token_seq, int t_first, int num_tokens, const float* sink,
+                                      cudaStream_t st);
 int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, long long num_pages,
                                  const int* block_table, int max_blocks, const int* cu_q_lens,
                                  const int* seq_lens, const int* tile_seq, const int* tile_start,
@@ -1152,6 +1183,19 @@ int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, lo
                                  int page_size, float scale, int window, int chunk_tiles, const int* tile_chunk, int max_chunks,
                                  float* part_o, float* part_ml, const int* token_seq, int t_first,
                                  int num_tokens, cudaStream_t st) {
+  return dib_extend_attention_tc_pair_sink(q, out, cache, num_pages, block_table, max_blocks, cu_q_lens, seq_lens,
+                                           tile_seq, tile_start, tile_start_b, num_tiles, Hq, Hkv, D, page_size,
+                                           scale, window, chunk_tiles, tile_chunk, max_chunks, part_o, part_ml,
+                                           token_seq, t_first, num_tokens, nullptr, st);
+}
+int dib_extend_attention_tc_pair_sink(const void* q, void* out, const void* cache, long long num_pages,
+                                      const int* block_table, int max_blocks, const int* cu_q_lens,
+                                      const int* seq_lens, const int* tile_seq, const int* tile_start,
+                                      const int* tile_start_b, int num_tiles, int Hq, int Hkv, int D,
+                                      int page_size, float scale, int window, int chunk_tiles,
+                                      const int* tile_chunk, int max_chunks, float* part_o, float* part_ml,
+                                      const int* token_seq, int t_first, int num_tokens, const float* sink,
+                                      cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
   if (D != TC_D || Hkv < 1 || Hq % Hkv != 0 || TC_M % (Hq / Hkv) != 0 || page_size < 8 ||
       page_size > TC_N || TC_N % page_size != 0 || num_tiles > 65535 ||
@@ -1178,12 +1222,12 @@ int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, lo
   dib_launch(extend_attention_tc_pair_kernel, dim3(Hkv, num_tiles), dim3(PAIR_THREADS), smem, st, *map,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens, seq_lens,
              tile_seq, tile_start, tile_start_b, Hq, Hkv, page_size, scale, window, chunk_tiles,
-             tile_chunk, max_chunks, part_o, part_ml);
+             tile_chunk, max_chunks, part_o, part_ml, sink);
   DIB_CHECK_LAUNCH();
   if (chunk_tiles > 0 && max_chunks > 1) {
     dib_launch(extend_attention_merge_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0, st,
                (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q_lens, seq_lens,
-               token_seq, t_first, num_tokens, Hq, Hkv, max_chunks, chunk_tiles, window);
+               token_seq, t_first, num_tokens, Hq, Hkv, max_chunks, chunk_tiles, window, sink);
     DIB_CHECK_LAUNCH();
   }
   return DIB_OK;

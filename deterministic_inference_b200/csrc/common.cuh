@@ -236,6 +236,15 @@ __device__ __forceinline__ void qk_row128(uint4& lo, uint4& hi, int l, unsigned 
   qk_row128_apply(lo, hi, nw != nullptr, rstd, wa, wb, rotate, c, sn);
 }
 
+// The oldest key a query at position pos sees.  window > 0: a sliding window of that many keys (the
+// query's own included); window < 0: the query's own chunk of -window positions, chunks counted from
+// position 0; 0: every key.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0 && pos > 0) return pos / (-window) * (-window);
+  return 0;
+}
+
 static inline int ceil_div_host(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // "Done once on the current device": a kernel's attributes (its shared-memory limit) are

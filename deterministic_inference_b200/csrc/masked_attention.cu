@@ -257,6 +257,20 @@ masked_attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
   }
 }
 
+// x[t, c] *= sigmoid(gate[t, gate_col + c]), in place; float32 arithmetic, one rounding
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, Source gate, long long gate_row, long long gate_col,
+                                    int rows, int width) {
+  pdl_prologue(x, gate.p);
+  const long long n = (long long)rows * width;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / width, c = i % width;
+    const float g = round_to<T>(source_load(gate, r * gate_row + gate_col + c));
+    Elem<T>::store(x + i, Elem<T>::load(x + i) * sigmoid_f32(g));
+  }
+}
+
 template <typename T>
 int launch_masked_attention(const void* q, void* out, const void* cache, const int* block_table,
                             int max_blocks, const int* token_seq, const int* positions, int T_tokens, int Hq,
@@ -346,6 +360,23 @@ int dib_heads_linear(const void* x, long long xs_m, long long xs_h, const void* 
     dib_launch(heads_linear_kernel<__nv_bfloat16>, grid, dim3(HL_COLS), smem, st, (const __nv_bfloat16*)x, xs_m,
                xs_h, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, os_m, os_h, M, K, N);
   } else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_sigmoid_gate_(void* x, const void* gate, int kind, int splits, long long stride, long long gate_row,
+                      long long gate_col, int rows, int width, int dtype, cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (width < 1) return DIB_BAD_SIZE;
+  const Source g = make_source(gate, kind, splits, stride);
+  const long long n = (long long)rows * width;
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  if (dtype == 0)
+    dib_launch(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, st, (float*)x, g, gate_row, gate_col, rows, width);
+  else if (dtype == 1)
+    dib_launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st, (__nv_bfloat16*)x, g, gate_row,
+               gate_col, rows, width);
+  else return DIB_BAD_DTYPE;
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

@@ -63,6 +63,16 @@ def _sm_count(device) -> int:
     return n
 
 
+def first_visible_key(pos: int, window: int) -> int:
+    """The oldest key a query at ``pos`` sees.  window > 0: a sliding window of that many keys;
+    window < 0: the query's own chunk of -window positions (chunks counted from 0); 0: every key."""
+    if window > 0:
+        return max(0, pos - window + 1)
+    if window < 0:
+        return pos // -window * -window
+    return 0
+
+
 def extend_chunk_units(q_lens: list, kv_lens: list, first_seq: int, tokens_per_tile: int,
                        chunk_tiles: int):
     """(sequence, first token of A, of B, chunk) for every chunk of ``chunk_tiles`` key tiles
@@ -110,13 +120,13 @@ def extend_tile_pairs(q_lens: list, kv_lens: list, first_seq: int, tokens_per_ti
         n = len(starts)
         if alone:
             pairs = [(a, -1) for a in starts]
-        elif window > 0 or neighbours:
+        elif window != 0 or neighbours:
             pairs = [(starts[i], starts[i + 1] if i + 1 < n else -1) for i in range(0, n, 2)]
         else:
             pairs = [(starts[i], starts[n - 1 - i] if n - 1 - i > i else -1) for i in range((n + 1) // 2)]
         for a, b in pairs:
             last = prefix + min(max(a, b) + tokens_per_tile, q_lens[s]) - 1
-            first = max(0, prefix + a - window + 1) if window > 0 else 0
+            first = first_visible_key(prefix + a, window)
             units.append((last // 128 - first // 128 + 1, s, a, b))
     units.sort()
     return [u[1] for u in units], [u[2] for u in units], [u[3] for u in units]
@@ -155,10 +165,11 @@ def _pair_lists(meta, nd: int, tpt: int, window: int, hkv: int, max_chunks: int,
     return (both[0], both[1], len(seqs), both[2]), None, (None, None)
 
 
-def run(q, out, kv_cache, meta, scale: float, window: int, defer: bool = False):
+def run(q, out, kv_cache, meta, scale: float, window: int, defer: bool = False, sink=None):
     """Fills ``out``; or, with ``defer`` and a step of one-token sequences only, returns an
     ``ops.SplitAttention`` (the decode kernel's partial results, not merged) and leaves
-    ``out`` alone."""
+    ``out`` alone.  ``window`` > 0: a sliding window of that many keys; < 0: chunks of -window
+    positions.  ``sink`` (float32 [Hq] or None): exp(sink[head]) joins the softmax's denominator."""
     from .ops import SplitAttention, _check, _lib, _ptr, _stream
 
     lib = _lib("attention_bf16")
@@ -174,13 +185,13 @@ def run(q, out, kv_cache, meta, scale: float, window: int, defer: bool = False):
                   torch.empty(nd, hq, max_splits, dtype=torch.float32, device=q.device))
             meta.scratch[("decode_ws", hq, d, max_splits)] = ws
         use_tma, pipelined = SWITCHES["decode_tma"], SWITCHES["decode_pipe"]
-        deferred = defer and nd == b and SWITCHES["defer_merge"]
-        st = lib.dib_decode_attention_bf16(
+        deferred = defer and nd == b and SWITCHES["defer_merge"] and sink is None
+        st = lib.dib_decode_attention_bf16_sink(
             _ptr(q), c_void_p(0) if deferred else _ptr(out), _ptr(kv_cache),
             c_longlong(kv_cache.shape[0] if use_tma else 0),
             _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
             _ptr(ws[0]), _ptr(ws[1]), c_int(nd), c_int(max_splits), c_int(hq), c_int(hkv), c_int(d),
-            c_int(page_size), c_float(scale), c_int(window), c_int(pipelined), _stream())
+            c_int(page_size), c_float(scale), c_int(window), c_int(pipelined), _ptr(sink), _stream())
         _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=1 if deferred else 2)
         if deferred:
             return SplitAttention(ws[0], ws[1], meta.seq_lens, nd, window, q.dtype)
@@ -199,11 +210,11 @@ def run(q, out, kv_cache, meta, scale: float, window: int, defer: bool = False):
                 both = torch.tensor([seqs, starts], dtype=torch.int32).to(q.device, non_blocking=True)
                 tiles = (both[0], both[1], len(seqs))
                 meta.scratch[("extend_tiles", tpt)] = tiles
-            st = tc_lib.dib_extend_attention_tc(
+            st = tc_lib.dib_extend_attention_tc_sink(
                 _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
                 c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
                 _ptr(tiles[1]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d), c_int(page_size),
-                c_float(scale), c_int(window), _stream())
+                c_float(scale), c_int(window), _ptr(sink), _stream())
             _check(st, "extend_attention_tc", f"heads {hq}/{hkv}, head_dim {d}")
             return
         # The lengths the host knows (under a captured graph an upper bound) say how many
@@ -212,18 +223,18 @@ def run(q, out, kv_cache, meta, scale: float, window: int, defer: bool = False):
         n_keys = max(meta.kv_lens[nd:])
         max_chunks = -(-n_keys // (CHUNK_TILES * 128))
         if max_chunks <= MAX_CHUNKS:
-            got = meta.scratch.get(("extend_pairs", tpt, window > 0))
+            got = meta.scratch.get(("extend_pairs", tpt, window))
             if got is None:
                 got = _pair_lists(meta, nd, tpt, window, hkv, max_chunks, t, hq, d, q.device)
-                meta.scratch[("extend_pairs", tpt, window > 0)] = got
+                meta.scratch[("extend_pairs", tpt, window)] = got
             tiles, chunk_list, ws = got
-            st = tc_lib.dib_extend_attention_tc_pair(
+            st = tc_lib.dib_extend_attention_tc_pair_sink(
                 _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
                 c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
                 _ptr(tiles[1]), _ptr(tiles[3]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d),
                 c_int(page_size), c_float(scale), c_int(window), c_int(CHUNK_TILES if max_chunks > 1 else 0),
                 _ptr(chunk_list), c_int(max_chunks), _ptr(ws[0]), _ptr(ws[1]), _ptr(meta.token_seq),
-                c_int(nd), c_int(t - nd), _stream())
+                c_int(nd), c_int(t - nd), _ptr(sink), _stream())
             _check(st, "extend_attention_tc_pair", f"heads {hq}/{hkv}, head_dim {d}",
                    kernels=2 if max_chunks > 1 else 1)
             return
@@ -236,8 +247,8 @@ def run(q, out, kv_cache, meta, scale: float, window: int, defer: bool = False):
             both = torch.tensor([seqs, starts], dtype=torch.int32).to(q.device, non_blocking=True)
             tiles = (both[0], both[1], len(seqs))
             meta.scratch[("extend_tiles", tpt)] = tiles
-        st = lib.dib_extend_attention_bf16(
+        st = lib.dib_extend_attention_bf16_sink(
             _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(bt), c_int(bt.shape[1]), _ptr(meta.cu_q_lens),
             _ptr(meta.seq_lens), _ptr(tiles[0]), _ptr(tiles[1]), c_int(tiles[2]), c_int(hq),
-            c_int(hkv), c_int(d), c_int(page_size), c_float(scale), c_int(window), _stream())
+            c_int(hkv), c_int(d), c_int(page_size), c_float(scale), c_int(window), _ptr(sink), _stream())
         _check(st, "extend_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}")

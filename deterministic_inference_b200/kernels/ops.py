@@ -1163,6 +1163,9 @@ def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> to
     return out
 
 
+# DIB200_MASKED_TC=0 (read once): bfloat16 steps run the float32-arithmetic attention kernel too
+MASKED_ATTENTION_TC = __import__("os").environ.get("DIB200_MASKED_TC", "1") != "0"
+
 # bfloat16 rows above which ``heads_linear`` is the library's batched product
 HEADS_LINEAR_LIBRARY_ROWS = 64
 
@@ -1197,6 +1200,22 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
     _need(meta.token_seq, "token_seq", torch.int32, 1)
     _need(meta.positions, "positions", torch.int32, 1)
     out = torch.empty(t, hq, v_head_dim, dtype=q.dtype, device=q.device)
+    if q.dtype == torch.bfloat16 and MASKED_ATTENTION_TC and not values_in_keys and dk == v_head_dim \
+            and getattr(meta, "q_lens", None) is not None and getattr(meta, "num_decode", None) is not None:
+        # keys and values of one size that the tensor-core kernels of ``attention_bf16`` take: the
+        # split-KV decode kernels for the step's one-token sequences, the tcgen05 kernel (heads of
+        # 128) or the mma.sync kernel for prompt portions; the mask goes in as a signed size, the sink
+        # into the last normalisation; the gate is a kernel of its own behind them
+        from . import attention_bf16
+        if attention_bf16.supports(hq, num_kv_heads, dk, page_size):
+            cache5 = kv_cache.view(kv_cache.shape[0], 2, num_kv_heads, page_size, dk)
+            attention_bf16.run(q, out, cache5, meta, scale, {0: 0, 1: size, 2: -size}[kind], False, sink)
+            if gate is not None:
+                st = _lib("masked_attention").dib_sigmoid_gate_(
+                    _ptr(out), *gate_args, c_longlong(gate_row), c_longlong(gate_col), c_int(t),
+                    c_int(hq * v_head_dim), c_int(_dt(q, "q")), _stream())
+                _check(st, "sigmoid_gate_")
+            return out
     st = _lib("masked_attention").dib_masked_attention(
         _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
         _ptr(meta.token_seq), _ptr(meta.positions), c_int(t), c_int(hq), c_int(num_kv_heads), c_int(dk),
