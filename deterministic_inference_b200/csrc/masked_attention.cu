@@ -381,6 +381,42 @@ int dib_sigmoid_gate_(void* x, const void* gate, int kind, int splits, long long
   return DIB_OK;
 }
 
+// The tensor-core form (bfloat16; Dk and Dv multiples of 16, Dv at most 256): tiles [num_tiles][3] =
+// (sequence, first token, tokens) of at most rows / (Hq / Hkv) tokens each; rows 64 or 128.
+// partial_o / partial_ml given (tiles of ONE token only): a token's key tiles are cut into chunks of
+// chunk_tiles, a CTA each, merged by a second kernel over the step's first num_tokens tokens.
+int dib_masked_attention_mma(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
+                             const int* positions, const int* seq_lens, const int* tiles, int num_tiles,
+                             const float* sink, int Hq, int Hkv, int Dk, int Dv, int Dv_stored, int page_size,
+                             float scale, int mask_kind, int mask_size, const void* gate, int gate_kind,
+                             int gate_splits, long long gate_stride, long long gate_row, long long gate_col,
+                             int rows, float* partial_o, float* partial_ml, int chunk_tiles, int max_chunks,
+                             int num_tokens, cudaStream_t st) {
+  if (num_tiles == 0) return DIB_OK;
+  if (Dk < 16 || Dk % 16 || Dv < 16 || Dv % 16 || Dv > 256 || Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > rows ||
+      (rows != 64 && rows != 128) || page_size < 1 || mask_kind < 0 || mask_kind > 2 ||
+      (mask_kind > 0 && mask_size < 1) || (Dv_stored != 0 && Dv_stored != Dv) || (Dv_stored == 0 && Dv > Dk) ||
+      num_tiles > 1 << 30 || Hkv > 65535 || max_chunks > 65535 || (partial_o != nullptr && chunk_tiles < 1))
+    return DIB_BAD_SIZE;
+  const Source g = make_source(gate, gate_kind, gate_splits, gate_stride);
+#define DIB_MAM(NV, ROWS)                                                                                    \
+  return ma_mma::launch<NV, ROWS>(q, out, cache, block_table, max_blocks, positions, seq_lens, tiles, num_tiles, \
+                                  sink, Hq, Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, g, \
+                                  gate_row, gate_col, partial_o, partial_ml, chunk_tiles, max_chunks, num_tokens, st)
+  const int nv = (Dv + 63) / 64;
+  if (rows == 64) {
+    if (nv == 1) DIB_MAM(4, 64);
+    if (nv == 2) DIB_MAM(8, 64);
+    if (nv == 3) DIB_MAM(12, 64);
+    DIB_MAM(16, 64);
+  }
+  if (nv == 1) DIB_MAM(4, 128);
+  if (nv == 2) DIB_MAM(8, 128);
+  if (nv == 3) DIB_MAM(12, 128);
+  DIB_MAM(16, 128);
+#undef DIB_MAM
+}
+
 // sink null: a plain softmax.  gate null: no output gate; else out *= sigmoid(gate[t, gate_col + h * Dv + d])
 // with rows gate_row elements apart.  Dv_stored 0: a key's first Dv elements are its value.
 int dib_masked_attention(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,

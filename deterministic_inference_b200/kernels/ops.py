@@ -1166,6 +1166,10 @@ def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> to
 # DIB200_MASKED_TC=0 (read once): bfloat16 steps run the float32-arithmetic attention kernel too
 MASKED_ATTENTION_TC = __import__("os").environ.get("DIB200_MASKED_TC", "1") != "0"
 
+# key tiles of 64 keys per CTA of a decoded token in the mma.sync form (a constant: where a token's
+# sums over its keys are cut depends on its position alone)
+MASKED_DECODE_CHUNK_TILES = 4
+
 # bfloat16 rows above which ``heads_linear`` is the library's batched product
 HEADS_LINEAR_LIBRARY_ROWS = 64
 
@@ -1215,6 +1219,51 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
                     _ptr(out), *gate_args, c_longlong(gate_row), c_longlong(gate_col), c_int(t),
                     c_int(hq * v_head_dim), c_int(_dt(q, "q")), _stream())
                 _check(st, "sigmoid_gate_")
+            return out
+    group = hq // num_kv_heads
+    if q.dtype == torch.bfloat16 and MASKED_ATTENTION_TC and dk % 16 == 0 and v_head_dim % 16 == 0 \
+            and v_head_dim <= 256 and group <= 128 and getattr(meta, "q_lens", None) is not None \
+            and getattr(meta, "num_decode", None) is not None and getattr(meta, "kv_lens", None) is not None:
+        # the mma.sync form for every other bfloat16 shape of sizes that are multiples of 16: the
+        # step's leading one-token sequences on tiles of one token whose keys are cut into chunks,
+        # a CTA each; prompt portions on tiles of 64 or 128 (token, head-of-group) rows
+        def smem_of(rows):
+            return 2 * ((rows + 128) * (dk + 8) + (0 if values_in_keys else 128 * (v_head_dim + 8)))
+        n_dec = meta.num_decode
+        rows = 128 if (group > 64 or max(meta.q_lens[n_dec:], default=0) * group > 64) else 64
+        if smem_of(rows) > 224 * 1024 and group <= 64:
+            rows = 64
+        dec_rows = 64 if group <= 64 else 128
+        if smem_of(rows) <= 224 * 1024 and smem_of(dec_rows) <= 224 * 1024:
+            key = ("masked_attention_tiles", group, rows)
+            lists = meta.scratch.get(key)
+            if lists is None:
+                lists = []
+                if n_dec:
+                    lists.append((dec_rows, True, sigmoid_attention_tiles(meta.q_lens[:n_dec], 1, q.device)))
+                if n_dec < len(meta.q_lens):
+                    lists.append((rows, False, sigmoid_attention_tiles(meta.q_lens, rows // group, q.device,
+                                                                       first=n_dec)))
+                meta.scratch[key] = lists
+            for form_rows, decoded, tiles in lists:
+                part_o = part_ml = None
+                max_chunks = 1
+                if decoded:
+                    # the most key tiles a decoded token can have
+                    most = (size // 64 + 2) if kind else (max(meta.kv_lens[:n_dec]) // 64 + 1)
+                    max_chunks = -(-most // MASKED_DECODE_CHUNK_TILES)
+                    if max_chunks > 1:
+                        part_o = torch.empty(n_dec, hq, max_chunks, v_head_dim, dtype=torch.float32, device=q.device)
+                        part_ml = torch.empty(n_dec, hq, max_chunks, 2, dtype=torch.float32, device=q.device)
+                st = _lib("masked_attention").dib_masked_attention_mma(
+                    _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
+                    _ptr(meta.positions), _ptr(meta.seq_lens), _ptr(tiles), c_int(tiles.shape[0]), _ptr(sink),
+                    c_int(hq), c_int(num_kv_heads), c_int(dk), c_int(v_head_dim), c_int(dv_stored),
+                    c_int(page_size), c_float(scale), c_int(kind), c_int(size), *gate_args, c_longlong(gate_row),
+                    c_longlong(gate_col), c_int(form_rows), _ptr(part_o), _ptr(part_ml),
+                    c_int(MASKED_DECODE_CHUNK_TILES), c_int(max_chunks), c_int(n_dec), _stream())
+                _check(st, "masked_attention(tensor cores)", f"heads {hq}/{num_kv_heads}, sizes {dk}/{v_head_dim}",
+                       kernels=2 if part_o is not None else 1)
             return out
     st = _lib("masked_attention").dib_masked_attention(
         _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),

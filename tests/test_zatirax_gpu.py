@@ -213,6 +213,9 @@ def test_latent_rows_and_the_products_per_head(dtype, heads, dim, rot, vdim, ran
     (4, 2, 64, 64, 16, "chunk", 64, True, True, False),
     (16, 1, 160, 128, 16, "window", 100, False, False, True),
     (5, 5, 20, 12, 8, "chunk", 7, True, True, False),       # a chunk shorter than a page
+    (4, 2, 32, 64, 16, "chunk", 50, True, True, False),     # values wider than keys on the tensor cores
+    (3, 1, 64, 192, 16, "window", 70, True, False, False),  # three rows a token, wide values
+    (24, 1, 96, 64, 8, "causal", None, False, False, True), # no mask: a decoded token's chunks grow with it
 ])
 def test_masked_attention_alone(dtype, heads, kv_heads, dk, dv, page, mask, size, sink, gate, in_keys):
     from deterministic_inference_b200.kernels import ops
