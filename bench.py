@@ -304,8 +304,36 @@ def gamilorn_like(q, layers: int, window: int, keep: int, r_heads: int, r_dim: i
         "max_positions": 8192, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": [layer] * layers})
 
 
+ZATIRAX_SIZES = {
+    # name -> the Zatirax mixer sizes that go with the Qwen3 preset of DESIGN_SIZES[name]: the attention
+    # layers take Qwen3's heads; the latent layers as many heads of 64 plain + 64 rotated dimensions
+    "0_6b": dict(chunk=1024, window=1024, rank=192, rot=64),
+    "8b": dict(chunk=4096, window=4096, rank=192, rot=64),
+}
+
+
+def zatirax_like(q, layers: int, chunk: int, window: int, rank: int, rot: int):
+    """A Zatirax configuration with the layer sizes of the Qwen3 configuration ``q``: an attention layer
+    and a latent-attention layer, run ``layers`` / 2 times in a row (one loop over both)."""
+    from deterministic_inference_b200.config.zatirax_config import ZatiraxConfig
+    d = q.head_dim
+    mlp = {"kind": "dense", "ff": q.intermediate_size, "limit": 7.0}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": q.num_attention_heads, "kv_heads": q.num_key_value_heads, "dim": d, "vdim": d,
+                     "scale": d ** -0.5, "mask": {"size": chunk},
+                     "rot": {"base": 500000.0, "dims": d // 2,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": q.num_attention_heads, "dim": d - rot, "rot_dim": rot, "vdim": d, "kv_rank": rank,
+                     "scale": d ** -0.5, "mask": {"size": window}, "rot": {"base": 10000.0, "dims": rot}}}
+    return ZatiraxConfig.from_dict({
+        "architecture": "Zatirax", "vocab": q.vocab_size, "width": q.hidden_size, "norm": {"eps": 1e-6},
+        "embedding": {"scale": 1.0}, "loop": {"start": 0, "stop": 2, "times": max(1, layers // 2)},
+        "layers": [att, lat]})
+
+
 def design_arm(a) -> int:
-    """``--design gamilorn``: prompt and decode throughput of the Gamilorn design at layer sizes of
+    """``--design zatirax``: the same for the Zatirax design.  ``--design gamilorn``: prompt and decode throughput of the Gamilorn design at layer sizes of
     real models (random weights, ``--design-layers`` layers), beside Qwen3 at the same sizes, and
     the new design's kernels one by one beside the like kernels of Qwen3, each with its share of
     the measured roofline.  Prints one JSON line of its own; the default benchmark is untouched."""
@@ -468,18 +496,118 @@ def design_arm(a) -> int:
                     cache.release_slot(sl)
         return rows
 
+    def zatirax_kernel_rows(eng_z, eng_q, zcfg, qcfg):
+        """Zatirax's kernels and the like kernels of Qwen3 on one layer's shapes: a prompt of ``n_prompt``
+        tokens, and a decode step of 8 requests with ``ctx`` cached tokens."""
+        rows = {}
+        hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        att, lat = zcfg.layers[0]["mixer"], zcfg.layers[1]["mixer"]
+        hq, hkv, d, w = att["heads"], att["kv_heads"], att["dim"], zcfg.width
+        chunk, win = att["mask"]["size"], lat["mask"]["size"]
+        lh, ld, lr, le, lc = lat["heads"], lat["dim"], lat["rot_dim"], lat["vdim"], lat["kv_rank"]
+        ff = zcfg.layers[0]["mlp"]["ff"]
+        bf = torch.bfloat16
+
+        def row(name, ms, nbytes, flops):
+            floor = max(nbytes / hbm, flops / tf) * 1e3
+            rows[name] = {"ms": round(ms, 4), "roofline_ms": round(floor, 4), "of_roofline": round(floor / ms, 4)}
+
+        for what, batch, q_len, before in (("prompt", 1, n_prompt, 0), ("decode_b8", 8, 1, ctx)):
+            t = batch * q_len
+            span = range(before, before + q_len)
+            for eng, mine in ((eng_z, True), (eng_q, False)):
+                runner, cache = eng.runner, eng.cache
+                slots = [cache.allocate_slot() for _ in range(batch)]
+                if before:
+                    for sl in slots:
+                        runner.step([SequenceInput(sl, prompt_of(1000, before), 0, [])])
+                entries = [SequenceInput(sl, [1] * q_len, before, []) for sl in slots]
+                for e_ in entries:
+                    cache.allocate(e_.slot, before + q_len)
+                cache.reset_fresh_state()
+                step = build_step_batch(entries, cache, dev)
+                q = torch.randn(t, hq, d, device=dev).to(bf)
+                one_w = torch.ones(w, device=dev)
+                if mine:
+                    kv, lkv = cache.view(0, step), cache.view(1, step)
+                    # chunked softmax attention with a sink (the tensor-core kernels Qwen3 runs on), then the gate
+                    keys = batch * sum(p % chunk + 1 for p in span)
+                    held = min(before + q_len, chunk)
+                    sink = torch.zeros(hq, device=dev)
+                    row(f"{what}: attention, chunk mask + sink", timed(lambda: ops.masked_attention(
+                        q, kv.kv, kv.attention_meta, d ** -0.5, hkv, d, kv.page_size, "chunk", chunk, sink)),
+                        2 * (2 * t * hq * d + batch * hkv * 2 * d * held), 4 * keys * hq * d)
+                    proj = torch.randn(t, (2 * hq + 2 * hkv) * d, device=dev)
+                    o = torch.randn(t, hq * d, device=dev).to(bf)
+                    from ctypes import c_int, c_longlong
+                    row(f"{what}: sigmoid gate on the heads", timed(lambda: ops._check(ops._lib("masked_attention").dib_sigmoid_gate_(
+                        ops._ptr(o), *ops._source_args(proj), c_longlong(proj.shape[1]), c_longlong((hq + 2 * hkv) * d),
+                        c_int(t), c_int(hq * d), c_int(1), ops._stream()), "gate")), t * hq * d * (2 + 2 + 4), 0)
+                    freq = runner.model.mixers[0].freq
+                    row(f"{what}: q/k norm + partial rotation + cache write", timed(lambda: ops.attn_prepare(
+                        proj, hq, hkv, d, d, one_w[:d].contiguous(), one_w[:d].contiguous(), 1e-6, freq, d // 2,
+                        step.positions, kv.kv, kv.slot_mapping, kv.page_size, bf)), t * (hq + 2 * hkv) * d * 6, 0)
+                    # latent attention: one key head of rank + rot, values read out of the keys
+                    ql = torch.randn(t, lh, lc + lr, device=dev).to(bf)
+                    keys = batch * sum(min(p + 1, win) for p in span)
+                    held = min(before + q_len, win)
+                    row(f"{what}: latent attention (window)", timed(lambda: ops.masked_attention(
+                        ql, lkv.kv, lkv.attention_meta, d ** -0.5, 1, lc, lkv.page_size, "window", win,
+                        values_in_keys=True)), 2 * (t * lh * (2 * lc + lr) + batch * (lc + lr) * held),
+                        2 * keys * lh * (2 * lc + lr))
+                    lproj = torch.randn(t, lh * (ld + lr) + lc + lr, device=dev).to(bf)
+                    mixer = runner.model.mixers[1]
+                    def latent_rows():
+                        qq = ops.latent_prepare(lproj, lh, ld, lr, lc, mixer.latent_norm, 1e-6, mixer.freq, step.positions,
+                                                lkv.kv, lkv.slot_mapping, lkv.page_size, bf)
+                        ops.heads_linear(lproj.as_strided((t, lh, ld), (lproj.shape[1], ld + lr, 1)), mixer.w_key, qq[:, :, :lc])
+                        oo = torch.empty(t, lh, le, dtype=bf, device=dev)
+                        ops.heads_linear(ql[:, :, :lc], mixer.w_value, oo)
+                    row(f"{what}: latent rows + the two products per head", timed(latent_rows),
+                        2 * (lproj.numel() + t * lh * (2 * lc + lr + le) + lh * lc * (ld + le)),
+                        2 * t * lh * lc * (ld + le))
+                    stream = torch.randn(t, w, device=dev)
+                    x0 = torch.randn(t, w, device=dev).to(bf)
+                    row(f"{what}: post norm + add + norm of the float32 stream", timed(lambda: ops.stream_rms_norm(
+                        stream, one_w, 1e-6, bf, add=ops.NormedTerm(x0, one_w, 1e-6))), t * w * (4 + 4 + 2 + 2), 0)
+                    gu = torch.randn(t, 2 * ff, device=dev)
+                    row(f"{what}: limited gate", timed(lambda: ops.limited_gate(gu, 7.0, 1.702, bf)), gu.numel() * 4 + t * ff * 2, 0)
+                else:
+                    view = cache.view(0, step)
+                    keys = batch * sum(p + 1 for p in span)
+                    row(f"{what}: qwen3 softmax attention", timed(lambda: ops.paged_attention(
+                        q, view.kv, view.attention_meta, d ** -0.5, None)),
+                        2 * (2 * t * hq * d + batch * hkv * 2 * d * (before + q_len)), 4 * keys * hq * d)
+                    x0 = torch.randn(t, w, device=dev).to(bf)
+                    res = torch.randn(t, w, device=dev).to(bf)
+                    row(f"{what}: qwen3 add + norm", timed(lambda: ops.add_rms_norm(x0, res, one_w, 1e-6)), t * w * 2 * 4, 0)
+                    gu = torch.randn(t, 2 * qcfg.intermediate_size, device=dev).to(bf)
+                    row(f"{what}: qwen3 silu gate", timed(lambda: ops.silu_mul(gu)), gu.numel() * 3, 0)
+                    qkv = torch.randn(t, (hq + 2 * hkv) * d, device=dev).to(bf)
+                    rope = runner.model.mixers[0].position_encoding.rotary_table()
+                    row(f"{what}: qwen3 q/k norm + rotation + cache write", timed(lambda: ops.qk_norm_rope_cache(
+                        qkv, hq, hkv, d, one_w[:d].contiguous(), one_w[:d].contiguous(), 1e-6, rope, step.positions,
+                        view.kv, view.slot_mapping, view.page_size)), qkv.numel() * 4, 0)
+                for sl in slots:
+                    cache.release_slot(sl)
+        return rows
+
     sampler = ClockSampler()
     sampler.start()
     sizes = {}
     for name in [x for x in a.design_sizes.split(",") if x.strip()]:
         preset_name, extra = DESIGN_SIZES[name]
         qcfg = preset(preset_name, num_hidden_layers=n_layers, max_window_layers=n_layers)
-        gcfg = gamilorn_like(qcfg, n_layers, **extra)
+        if a.design == "zatirax":
+            extra = ZATIRAX_SIZES[name]
+            gcfg = zatirax_like(qcfg, n_layers, **extra)
+        else:
+            gcfg = gamilorn_like(qcfg, n_layers, **extra)
         out = {"layers": n_layers, "width": qcfg.hidden_size, "heads": f"{qcfg.num_attention_heads}/{qcfg.num_key_value_heads} x {qcfg.head_dim}",
-               "ff": qcfg.intermediate_size, "gamilorn": dict(extra, parameters=gcfg.num_parameters()),
+               "ff": qcfg.intermediate_size, a.design: dict(extra, parameters=gcfg.num_parameters()),
                "qwen3_parameters": qcfg.num_parameters()}
         engines = {}
-        for label, mcfg in (("gamilorn", gcfg), ("qwen3", qcfg)):
+        for label, mcfg in ((a.design, gcfg), ("qwen3", qcfg)):
             eng = engines[label] = engine_for(mcfg)
             ms = prefill_ms(eng, mcfg.vocab_size)
             r = {"prefill_ms": round(ms, 3), "prefill_tok_s": round(n_prompt / (ms / 1e3))}
@@ -488,13 +616,14 @@ def design_arm(a) -> int:
                 r[f"decode_b{b}_ms"] = round(dms, 4)
                 r[f"decode_b{b}_tok_s"] = round(b / (dms / 1e3))
             out[label + "_result"] = r
-        out["kernels"] = kernel_rows(engines["gamilorn"], engines["qwen3"], gcfg, qcfg)
+        rows_of = zatirax_kernel_rows if a.design == "zatirax" else kernel_rows
+        out["kernels"] = rows_of(engines[a.design], engines["qwen3"], gcfg, qcfg)
         sizes[name] = out
         del engines
         import gc
         gc.collect()
         torch.cuda.empty_cache()
-    print(json.dumps({"metric": "gamilorn beside qwen3 at equal layer sizes (bf16, 1 B200)", "impl": "ours",
+    print(json.dumps({"metric": f"{a.design} beside qwen3 at equal layer sizes (bf16, 1 B200)", "impl": "ours",
                       "dtype": "bf16", "data": "synthetic, random weights", "n_gpus": 1,
                       "prompt_tokens": n_prompt, "decode_context": ctx, "decode_steps": a.point_steps,
                       "warmup": a.warmup, "l2": "flushed before every timed kernel; steps hold more than L2",
@@ -528,7 +657,7 @@ def main() -> int:
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="bracket this region with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); the numbers of such a run are not a result")
-    ap.add_argument("--design", default=None, choices=["gamilorn"],
+    ap.add_argument("--design", default=None, choices=["gamilorn", "zatirax"],
                     help="measure this design beside Qwen3 at equal layer sizes instead of the default "
                          "workload (prints a line of its own)")
     ap.add_argument("--design-sizes", default="0_6b,8b", help=f"of {sorted(DESIGN_SIZES)}")

@@ -100,8 +100,8 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 template <int D, int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV,
                                              const __nv_bfloat16* __restrict__ cache,
-                                             const int* __restrict__ bt, int k0, int nkeys,
-                                             int kv_len, int kvh, int Hkv, int page_size) {
+                                             const int* __restrict__ bt, int max_blocks, int k0,
+                                             int nkeys, int kv_len, int kvh, int Hkv, int page_size) {
   constexpr int CH = D / 8;  // 16-byte chunks per row
   const size_t head_stride = (size_t)page_size * D;
   const size_t kv_stride = (size_t)Hkv * head_stride;
@@ -111,7 +111,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* s
     const bool valid = key < kv_len;
     const __nv_bfloat16* src = cache;
     if (valid) {
-      const int page = bt[key / page_size];
+      // (a key beyond the table's width, a padding sequence's, reads page 0)
+      const int page = key / page_size < max_blocks ? bt[key / page_size] : 0;
       src = cache + (size_t)page * 2 * kv_stride + (size_t)kvh * head_stride +
             (size_t)(key % page_size) * D + ch * 8;
     }
@@ -276,7 +277,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
   const int first_key = first_visible_key(first_pos, window);
   const int j0 = first_key / EXT_N, j1 = last_pos / EXT_N;
 
-  load_kv_tile<D, EXT_THREADS>(sK0, sK0 + TILE_ELEMS, cache, bt, j0 * EXT_N, EXT_N, kv_len, kvh, Hkv,
+  load_kv_tile<D, EXT_THREADS>(sK0, sK0 + TILE_ELEMS, cache, bt, max_blocks, j0 * EXT_N, EXT_N, kv_len, kvh, Hkv,
                                page_size);
   cp_async_commit();
   __syncthreads();  // sQ visible
@@ -317,7 +318,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     __nv_bfloat16* sV = sK + TILE_ELEMS;
     if (j + 1 <= j1) {
       __nv_bfloat16* nK = sK0 + (stage ^ 1) * 2 * TILE_ELEMS;
-      load_kv_tile<D, EXT_THREADS>(nK, nK + TILE_ELEMS, cache, bt, (j + 1) * EXT_N, EXT_N, kv_len,
+      load_kv_tile<D, EXT_THREADS>(nK, nK + TILE_ELEMS, cache, bt, max_blocks, (j + 1) * EXT_N, EXT_N, kv_len,
                                    kvh, Hkv, page_size);
       cp_async_commit();
       cp_async_wait<1>();
@@ -405,7 +406,7 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
       const int key = k0 + r;
       const size_t head_stride = (size_t)page_size * D;
       const size_t kv_stride = (size_t)Hkv * head_stride;
-      const int page = bt[key / page_size];
+      const int page = key / page_size < max_blocks ? bt[key / page_size] : 0;
       const __nv_bfloat16* src = cache + (size_t)page * 2 * kv_stride + (size_t)kvh * head_stride +
                                  (size_t)(key % page_size) * D;
       bulk_g2s(dk, src, D * 2, &bars[0]);

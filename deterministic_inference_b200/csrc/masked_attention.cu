@@ -147,33 +147,52 @@ latent_prepare_kernel(Source proj, long long row_width, T* __restrict__ q_out, T
 
 // ---- a product per head --------------------------------------------------------------------------
 // out[m, h, n] = sum_k x[m, h, k] * w[h, k, n]; x and out with free row and head strides (elements),
-// w contiguous [H, K, N].  float32 accumulation, k ascending: a row's bits depend on nothing else.
-constexpr int HL_ROWS = 8, HL_COLS = 128;
+// w contiguous [H, K, N].  float32 accumulation.  A block takes HL_ROWS rows and HL_COLS columns of one
+// head; k is cut into HL_SLICES equal runs, a group of threads each (so that few rows still keep many
+// loads of the weights in flight), every run added up in ascending k and the runs' sums in run order:
+// a row's bits depend on K alone.
+constexpr int HL_ROWS = 8, HL_COLS = 64, HL_SLICES = 4;
 template <typename T>
-__global__ void __launch_bounds__(HL_COLS)
+__global__ void __launch_bounds__(HL_COLS * HL_SLICES)
 heads_linear_kernel(const T* __restrict__ x, long long xs_m, long long xs_h, const T* __restrict__ w,
                     T* __restrict__ out, long long os_m, long long os_h, int M, int K, int N) {
-  extern __shared__ float xs[];      // [HL_ROWS][K]
+  extern __shared__ float xs[];      // [HL_ROWS][K], then the runs' sums [HL_SLICES][HL_ROWS][HL_COLS]
+  float* part = xs + (size_t)HL_ROWS * K;
   pdl_prologue(x);
-  const int h = blockIdx.y, m0 = blockIdx.z * HL_ROWS, n = blockIdx.x * HL_COLS + threadIdx.x;
+  const int h = blockIdx.y, m0 = blockIdx.z * HL_ROWS;
+  const int col = threadIdx.x % HL_COLS, run = threadIdx.x / HL_COLS;
+  const int n = blockIdx.x * HL_COLS + col;
   const int rows = M - m0 < HL_ROWS ? M - m0 : HL_ROWS;
-  for (int i = threadIdx.x; i < HL_ROWS * K; i += HL_COLS) {
+  for (int i = threadIdx.x; i < HL_ROWS * K; i += HL_COLS * HL_SLICES) {
     const int r = i / K, k = i % K;
     xs[i] = r < rows ? Elem<T>::load(x + (long long)(m0 + r) * xs_m + (long long)h * xs_h + k) : 0.f;
   }
   __syncthreads();
-  if (n >= N) return;
   float acc[HL_ROWS];
 #pragma unroll
   for (int r = 0; r < HL_ROWS; ++r) acc[r] = 0.f;
-  const T* wp = w + (long long)h * K * N + n;
-  for (int k = 0; k < K; ++k) {
-    const float wv = Elem<T>::load(wp + (long long)k * N);
+  const int per = (K + HL_SLICES - 1) / HL_SLICES;
+  const int k_begin = run * per, k_end = k_begin + per < K ? k_begin + per : K;
+  if (n < N) {
+    const T* wp = w + (long long)h * K * N + n;
+#pragma unroll 8
+    for (int k = k_begin; k < k_end; ++k) {
+      const float wv = Elem<T>::load(wp + (long long)k * N);
 #pragma unroll
-    for (int r = 0; r < HL_ROWS; ++r) acc[r] = __fmaf_rn(xs[r * K + k], wv, acc[r]);
+      for (int r = 0; r < HL_ROWS; ++r) acc[r] = __fmaf_rn(xs[r * K + k], wv, acc[r]);
+    }
   }
-  for (int r = 0; r < rows; ++r)
-    Elem<T>::store(out + (long long)(m0 + r) * os_m + (long long)h * os_h + n, acc[r]);
+#pragma unroll
+  for (int r = 0; r < HL_ROWS; ++r) part[(run * HL_ROWS + r) * HL_COLS + col] = acc[r];
+  __syncthreads();
+  if (run == 0 && n < N) {
+    for (int r = 0; r < rows; ++r) {
+      float v = part[r * HL_COLS + col];
+#pragma unroll
+      for (int s = 1; s < HL_SLICES; ++s) v = __fadd_rn(v, part[(s * HL_ROWS + r) * HL_COLS + col]);
+      Elem<T>::store(out + (long long)(m0 + r) * os_m + (long long)h * os_h + n, v);
+    }
+  }
 }
 
 // ---- attention, float32 arithmetic ----------------------------------------------------------------
@@ -215,7 +234,8 @@ masked_attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
     float s = NEG_BIG;
     const T* vrow = nullptr;
     if (visible) {
-      const T* page = cache + (size_t)bt[key / page_size] * page_elems;
+      // (a key beyond the table's width, a padding sequence's, reads page 0)
+      const T* page = cache + (size_t)(key / page_size < max_blocks ? bt[key / page_size] : 0) * page_elems;
       const size_t in_page = (size_t)kvh * page_size + key % page_size;
       const T* krow = page + in_page * Dk;
       vrow = Dv_stored > 0 ? page + values_at + in_page * Dv : krow;
@@ -348,16 +368,16 @@ int dib_heads_linear(const void* x, long long xs_m, long long xs_h, const void* 
   if (H < 1 || H > 65535 || K < 1 || K > 4096 || N < 1) return DIB_BAD_SIZE;
   const dim3 grid(ceil_div_host(N, HL_COLS), H, ceil_div_host(M, HL_ROWS));
   if (grid.z > 65535) return DIB_BAD_SIZE;
-  const size_t smem = (size_t)HL_ROWS * K * sizeof(float);
+  const size_t smem = ((size_t)HL_ROWS * K + (size_t)HL_SLICES * HL_ROWS * HL_COLS) * sizeof(float);
   if (dtype == 0) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(heads_linear_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    dib_launch(heads_linear_kernel<float>, grid, dim3(HL_COLS), smem, st, (const float*)x, xs_m, xs_h,
+    dib_launch(heads_linear_kernel<float>, grid, dim3(HL_COLS * HL_SLICES), smem, st, (const float*)x, xs_m, xs_h,
                (const float*)w, (float*)out, os_m, os_h, M, K, N);
   } else if (dtype == 1) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(heads_linear_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    dib_launch(heads_linear_kernel<__nv_bfloat16>, grid, dim3(HL_COLS), smem, st, (const __nv_bfloat16*)x, xs_m,
+    dib_launch(heads_linear_kernel<__nv_bfloat16>, grid, dim3(HL_COLS * HL_SLICES), smem, st, (const __nv_bfloat16*)x, xs_m,
                xs_h, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, os_m, os_h, M, K, N);
   } else return DIB_BAD_DTYPE;
   DIB_CHECK_LAUNCH();
@@ -382,12 +402,13 @@ int dib_sigmoid_gate_(void* x, const void* gate, int kind, int splits, long long
 }
 
 // The tensor-core form (bfloat16; Dk and Dv multiples of 16, Dv at most 256): tiles [num_tiles][3] =
-// (sequence, first token, tokens) of at most rows / (Hq / Hkv) tokens each; rows 64 or 128.
+// (sequence, first token among the sequence's new tokens, tokens) of at most rows / (Hq / Hkv) tokens
+// each; rows 64 or 128.
 // partial_o / partial_ml given (tiles of ONE token only): a token's key tiles are cut into chunks of
 // chunk_tiles, a CTA each, merged by a second kernel over the step's first num_tokens tokens.
 int dib_masked_attention_mma(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
-                             const int* positions, const int* seq_lens, const int* tiles, int num_tiles,
-                             const float* sink, int Hq, int Hkv, int Dk, int Dv, int Dv_stored, int page_size,
+                             const int* positions, const int* seq_lens, const int* cu_q_lens, const int* tiles,
+                             int num_tiles, const float* sink, int Hq, int Hkv, int Dk, int Dv, int Dv_stored, int page_size,
                              float scale, int mask_kind, int mask_size, const void* gate, int gate_kind,
                              int gate_splits, long long gate_stride, long long gate_row, long long gate_col,
                              int rows, float* partial_o, float* partial_ml, int chunk_tiles, int max_chunks,
@@ -400,7 +421,7 @@ int dib_masked_attention_mma(const void* q, void* out, const void* cache, const 
     return DIB_BAD_SIZE;
   const Source g = make_source(gate, gate_kind, gate_splits, gate_stride);
 #define DIB_MAM(NV, ROWS)                                                                                    \
-  return ma_mma::launch<NV, ROWS>(q, out, cache, block_table, max_blocks, positions, seq_lens, tiles, num_tiles, \
+  return ma_mma::launch<NV, ROWS>(q, out, cache, block_table, max_blocks, positions, seq_lens, cu_q_lens, tiles, num_tiles, \
                                   sink, Hq, Hkv, Dk, Dv, Dv_stored, page_size, scale, mask_kind, mask_size, g, \
                                   gate_row, gate_col, partial_o, partial_ml, chunk_tiles, max_chunks, num_tokens, st)
   const int nv = (Dv + 63) / 64;

@@ -43,13 +43,17 @@ __device__ __forceinline__ int first_seen(int pos, int mask_kind, int mask_size)
   return 0;
 }
 
-// tiles: int32 [n][3] = (sequence of the step, first token of the tile in the step, tokens).
+// tiles: int32 [n][3] = (sequence of the step, first token of the tile among the sequence's new tokens,
+// tokens at most).  Where the sequence's tokens lie in the step and how many it really brings is read
+// on the device (cu_q_lens): a list made for upper bounds (a captured graph's) names tiles past a
+// sequence's real tokens, which leave at once.
 // NV16: value columns in units of 16 the accumulators are sized for (VD <= 16 * NV16).
 template <int NV16, int ROWS>
 __global__ void __launch_bounds__(ROWS * 2)
 masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __nv_bfloat16* cache,
                             const int* block_table, int bt_width, const int* positions, const int* seq_lens,
-                            const int* tiles, const float* sink, int Hq, int Hkv, int D, int VD, int VD_stored,
+                            const int* cu_q_lens, const int* tiles, const float* sink, int Hq, int Hkv, int D,
+                            int VD, int VD_stored,
                             int page_size, float scale, int mask_kind, int mask_size, Source gate,
                             long long gate_row, long long gate_col, float* partial_o, float* partial_ml,
                             int chunk_tiles, int max_chunks) {
@@ -63,7 +67,11 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
   __shared__ long long k_off[2][KT], v_off[2][KT];
   pdl_prologue(q, cache, gate.p);
   const int tile = blockIdx.x, g = blockIdx.y;
-  const int b = tiles[3 * tile], t0 = tiles[3 * tile + 1], count = tiles[3 * tile + 2];
+  const int b = tiles[3 * tile], start = tiles[3 * tile + 1];
+  const int q_begin = cu_q_lens[b], q_len = cu_q_lens[b + 1] - q_begin;
+  if (start >= q_len) return;               // (the whole CTA: the sequence brings fewer tokens)
+  const int t0 = q_begin + start;
+  const int count = tiles[3 * tile + 2] < q_len - start ? tiles[3 * tile + 2] : q_len - start;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int kv_len = seq_lens[b];
@@ -94,7 +102,8 @@ masked_attention_mma_kernel(const __nv_bfloat16* q, __nv_bfloat16* out, const __
       const int j = (t_first + it) * KT + threadIdx.x;
       long long ko = -1, vo = -1;
       if (j < kv_len) {
-        const long long base = (long long)bt[j / page_size] * page_elems;
+        // (a key beyond the table's width, a padding sequence's, reads page 0)
+        const long long base = (long long)(j / page_size < bt_width ? bt[j / page_size] : 0) * page_elems;
         const long long r = (long long)g * page_size + j % page_size;
         ko = base + r * D;
         vo = base + (long long)Hkv * page_size * D + r * VD;
@@ -335,8 +344,8 @@ static inline size_t smem_bytes(int D, int VD, int VD_stored, int rows) {
 
 template <int NV16, int ROWS>
 static int launch(const void* q, void* out, const void* cache, const int* block_table, int bt_width,
-                  const int* positions, const int* seq_lens, const int* tiles, int num_tiles, const float* sink,
-                  int Hq, int Hkv, int D, int VD, int VD_stored, int page_size, float scale, int mask_kind,
+                  const int* positions, const int* seq_lens, const int* cu_q_lens, const int* tiles, int num_tiles,
+                  const float* sink, int Hq, int Hkv, int D, int VD, int VD_stored, int page_size, float scale, int mask_kind,
                   int mask_size, Source gate, long long gate_row, long long gate_col, float* partial_o,
                   float* partial_ml, int chunk_tiles, int max_chunks, int num_tokens, cudaStream_t st) {
   const size_t smem = smem_bytes(D, VD, VD_stored, ROWS);
@@ -351,7 +360,7 @@ static int launch(const void* q, void* out, const void* cache, const int* block_
   }
   dib_launch(masked_attention_mma_kernel<NV16, ROWS>, dim3(num_tiles, Hkv, chunked ? max_chunks : 1), dim3(ROWS * 2),
              smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, block_table,
-             bt_width, positions, seq_lens, tiles, sink, Hq, Hkv, D, VD, VD_stored, page_size, scale, mask_kind,
+             bt_width, positions, seq_lens, cu_q_lens, tiles, sink, Hq, Hkv, D, VD, VD_stored, page_size, scale, mask_kind,
              mask_size, gate, gate_row, gate_col, chunked ? partial_o : (float*)nullptr,
              chunked ? partial_ml : (float*)nullptr, chunk_tiles, max_chunks);
   DIB_CHECK_LAUNCH();

@@ -32,34 +32,75 @@ __global__ void embed_scale_kernel(const void* table, int dtype, const int* ids,
 // One block per row: residual[row] += x[row] / sqrt(mean(x[row]^2) + eps_x) * wx (+ bias), the
 // normed output of the part before added to the stream without being rounded; then, when out is
 // given, out[row] = residual[row] / sqrt(mean(residual[row]^2) + eps) * w.  x null: only the bias
-// is added.
+// is added.  VPT > 0: a thread keeps its VPT elements of the row in registers (W <= VPT * blockDim.x),
+// so the row is read once; VPT == 0: any width, the row is read again for every pass.  Both add a
+// row's squares in the same order (a thread its own elements in ascending order, then the block's sum).
+template <int VPT>
 __global__ void stream_normed_add_kernel(float* residual, Source x, const float* wx, float eps_x,
                                          const float* bias, const float* w, void* out, int out_dtype,
                                          int W, float eps) {
   __shared__ float scratch[32];
   pdl_prologue(x.p);
   const long long base = (long long)blockIdx.x * W;
+  constexpr int N = VPT > 0 ? VPT : 1;
+  float xv[N], rv[N];
   float rx = 0.f;
+  if (VPT > 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      xv[i] = (x.p != nullptr && c < W) ? source_load(x, base + c) : 0.f;
+      rv[i] = c < W ? residual[base + c] : 0.f;
+    }
+  }
   if (x.p != nullptr) {
     float sx = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-      const float v = source_load(x, base + c);
-      sx = __fmaf_rn(v, v, sx);
+    if (VPT > 0) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) sx = __fmaf_rn(xv[i], xv[i], sx);
+    } else {
+      for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = source_load(x, base + c);
+        sx = __fmaf_rn(v, v, sx);
+      }
     }
     rx = 1.0f / sqrtf(block_sum(sx, scratch) / (float)W + eps_x);
   }
   float ss = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float r = residual[base + c];
-    if (x.p != nullptr) r = __fadd_rn(r, source_load(x, base + c) * rx * wx[c]);
-    if (bias != nullptr) r = __fadd_rn(r, bias[c]);
-    residual[base + c] = r;
-    ss = __fmaf_rn(r, r, ss);
+  if (VPT > 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < W) {
+        float r = rv[i];
+        if (x.p != nullptr) r = __fadd_rn(r, xv[i] * rx * wx[c]);
+        if (bias != nullptr) r = __fadd_rn(r, bias[c]);
+        residual[base + c] = r;
+        rv[i] = r;
+        ss = __fmaf_rn(r, r, ss);
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      float r = residual[base + c];
+      if (x.p != nullptr) r = __fadd_rn(r, source_load(x, base + c) * rx * wx[c]);
+      if (bias != nullptr) r = __fadd_rn(r, bias[c]);
+      residual[base + c] = r;
+      ss = __fmaf_rn(r, r, ss);
+    }
   }
   if (out == nullptr) return;
   const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)W + eps);
-  for (int c = threadIdx.x; c < W; c += blockDim.x)
-    store_as(out, out_dtype, base + c, residual[base + c] * rstd * w[c]);
+  if (VPT > 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < W) store_as(out, out_dtype, base + c, rv[i] * rstd * w[c]);
+    }
+  } else {
+    for (int c = threadIdx.x; c < W; c += blockDim.x)
+      store_as(out, out_dtype, base + c, residual[base + c] * rstd * w[c]);
+  }
 }
 
 // [gate | up] rows of width 2I -> I: g = min(gate, limit), u = clamp(up, -limit, limit),
@@ -170,8 +211,15 @@ int dib_stream_normed_add(float* residual, const void* x, int kind, int splits, 
   if (W < 1) return DIB_BAD_SIZE;
   if (out != nullptr && out_dtype != 0 && out_dtype != 1) return DIB_BAD_DTYPE;
   const dim3 grid(rows), block(W >= 2048 ? 512 : (W >= 512 ? 256 : 128));
-  dib_launch(stream_normed_add_kernel, grid, block, 0, st, residual, make_source(x, kind, splits, stride), wx,
-             eps_x, bias, w, out, out_dtype, W, eps);
+  const Source src = make_source(x, kind, splits, stride);
+  const int per_thread = (W + (int)block.x - 1) / (int)block.x;
+#define DIB_SNA(VPT) \
+  dib_launch(stream_normed_add_kernel<VPT>, grid, block, 0, st, residual, src, wx, eps_x, bias, w, out, out_dtype, W, eps)
+  if (per_thread <= 4) DIB_SNA(4);
+  else if (per_thread <= 8) DIB_SNA(8);
+  else if (per_thread <= 16) DIB_SNA(16);
+  else DIB_SNA(0);
+#undef DIB_SNA
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

@@ -1062,6 +1062,20 @@ def _mask_args(mask: str, size) -> tuple:
     return MASK_KINDS[mask], int(size) if mask != "causal" else 0
 
 
+def sequence_tiles(q_lens: list, tokens_per_tile: int, device, first: int = 0, last=None) -> torch.Tensor:
+    """int32 [n, 3] on ``device``: (sequence, first token of the tile among the sequence's new tokens,
+    tokens) for every run of up to ``tokens_per_tile`` consecutive tokens of the sequences ``first`` ..
+    ``last`` - 1.  The lengths may be upper bounds (a captured graph's): the kernel reads the real ones on
+    the device and drops what lies beyond them."""
+    rows = [(b, k, min(tokens_per_tile, q_lens[b] - k))
+            for b in range(first, len(q_lens) if last is None else last)
+            for k in range(0, q_lens[b], tokens_per_tile)]
+    host = torch.tensor(rows, dtype=torch.int32).view(-1, 3)
+    if torch.device(device).type == "cuda":
+        return host.pin_memory().to(device, non_blocking=True)
+    return host
+
+
 def _cache_pages(kv_cache, page_elems: int, what: str) -> int:
     if kv_cache.numel() % page_elems or kv_cache.shape[0] != kv_cache.numel() // page_elems:
         raise KernelError(f"{what}: cache of shape {tuple(kv_cache.shape)} is not [pages, ...] of pages of "
@@ -1165,13 +1179,16 @@ def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> to
 
 # DIB200_MASKED_TC=0 (read once): bfloat16 steps run the float32-arithmetic attention kernel too
 MASKED_ATTENTION_TC = __import__("os").environ.get("DIB200_MASKED_TC", "1") != "0"
+# DIB200_MASKED_MMA=0 (read once): only the mma.sync form of this module is left out
+MASKED_ATTENTION_MMA = __import__("os").environ.get("DIB200_MASKED_MMA", "1") != "0"
 
 # key tiles of 64 keys per CTA of a decoded token in the mma.sync form (a constant: where a token's
 # sums over its keys are cut depends on its position alone)
-MASKED_DECODE_CHUNK_TILES = 4
+MASKED_DECODE_CHUNK_TILES = 2
 
-# bfloat16 rows above which ``heads_linear`` is the library's batched product
-HEADS_LINEAR_LIBRARY_ROWS = 64
+# bfloat16 rows above which ``heads_linear`` is the library's batched product (DIB200_HEADS_LINEAR_ROWS,
+# read once)
+HEADS_LINEAR_LIBRARY_ROWS = int(__import__("os").environ.get("DIB200_HEADS_LINEAR_ROWS", "64"))
 
 
 def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float, num_kv_heads: int,
@@ -1221,7 +1238,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
                 _check(st, "sigmoid_gate_")
             return out
     group = hq // num_kv_heads
-    if q.dtype == torch.bfloat16 and MASKED_ATTENTION_TC and dk % 16 == 0 and v_head_dim % 16 == 0 \
+    if q.dtype == torch.bfloat16 and MASKED_ATTENTION_TC and MASKED_ATTENTION_MMA and dk % 16 == 0 and v_head_dim % 16 == 0 \
             and v_head_dim <= 256 and group <= 128 and getattr(meta, "q_lens", None) is not None \
             and getattr(meta, "num_decode", None) is not None and getattr(meta, "kv_lens", None) is not None:
         # the mma.sync form for every other bfloat16 shape of sizes that are multiples of 16: the
@@ -1240,10 +1257,9 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
             if lists is None:
                 lists = []
                 if n_dec:
-                    lists.append((dec_rows, True, sigmoid_attention_tiles(meta.q_lens[:n_dec], 1, q.device)))
+                    lists.append((dec_rows, True, sequence_tiles(meta.q_lens, 1, q.device, last=n_dec)))
                 if n_dec < len(meta.q_lens):
-                    lists.append((rows, False, sigmoid_attention_tiles(meta.q_lens, rows // group, q.device,
-                                                                       first=n_dec)))
+                    lists.append((rows, False, sequence_tiles(meta.q_lens, rows // group, q.device, first=n_dec)))
                 meta.scratch[key] = lists
             for form_rows, decoded, tiles in lists:
                 part_o = part_ml = None
@@ -1257,7 +1273,8 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
                         part_ml = torch.empty(n_dec, hq, max_chunks, 2, dtype=torch.float32, device=q.device)
                 st = _lib("masked_attention").dib_masked_attention_mma(
                     _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
-                    _ptr(meta.positions), _ptr(meta.seq_lens), _ptr(tiles), c_int(tiles.shape[0]), _ptr(sink),
+                    _ptr(meta.positions), _ptr(meta.seq_lens), _ptr(meta.cu_q_lens), _ptr(tiles),
+                    c_int(tiles.shape[0]), _ptr(sink),
                     c_int(hq), c_int(num_kv_heads), c_int(dk), c_int(v_head_dim), c_int(dv_stored),
                     c_int(page_size), c_float(scale), c_int(kind), c_int(size), *gate_args, c_longlong(gate_row),
                     c_longlong(gate_col), c_int(form_rows), _ptr(part_o), _ptr(part_ml),

@@ -46,7 +46,7 @@ class GatedMLP(FeedForward):
     def forward(self, x):
         if self.activation == "silu":
             return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down)
-        gate_up = ops.linear(x, self.w_gate_up, out_dtype=torch.float32 if x.dtype != torch.float32 else None)
+        gate_up = ops.linear(x, self.w_gate_up)       # (few rows: split-k partial sums, added in float32 by the gate)
         return ops.linear(ops.limited_gate(gate_up, self.limit, self.alpha, self.out_dtype), self.w_down)
 
 

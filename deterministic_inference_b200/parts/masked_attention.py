@@ -87,8 +87,8 @@ class MaskedAttention(Mixer):
                            mask="chunk" if self.mask == "chunk" else "window")
 
     def forward(self, x, step, cache):
-        # the projection's float32 accumulator is what the norm, the rotation and the gate read
-        proj = ops.linear(x, self.w_in, out_dtype=torch.float32 if x.dtype != torch.float32 else None)
+        # (few rows: the product's split-k partial sums, which the readers add in float32 while they load)
+        proj = ops.linear(x, self.w_in)
         q = ops.attn_prepare(proj, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim,
                              self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.freq, self.rotary_dim,
                              step.positions, cache.kv if cache.writes else None, cache.slot_mapping,

@@ -376,6 +376,42 @@ def test_replay_all_cuttings(name, dtype, model_dirs, plain_logits, tmp_path):
     print(f"{name}/{dtype}: worst difference {worst:.3e} of the logits' spread")
 
 
+@pytest.mark.parametrize("name, dtype", [("z4", "bfloat16"), ("z1", "bfloat16"), ("z3", "float32")])
+def test_replay_with_captured_graphs(name, dtype, model_dirs, tmp_path):
+    """The step function as generation runs it: pure-decode steps and steps whose shape has come twice
+    before are replayed as captured CUDA graphs, whose kernels size their grids and tile lists for the
+    bucket's upper bounds and read the real lengths on the device.  Four requests of one length, cut
+    alike, so that every shape repeats, and the mixed cutting on top; the replayed run against a launched
+    run of the same trace (equal bits: every product is kept on the kernels whose sums do not depend on
+    the row count) and against the plain implementation."""
+    cfg, w = pz.read_model_dir(model_dirs[name])
+    same = zu.requests(cfg["vocab"], [330] * 4, 41)
+    other = zu.requests(cfg["vocab"], [33, 150, 77], 42)
+    reqs = same + other
+    exact = [pz.forward(cfg, w, r) for r in reqs]
+    stored = [pz.forward(cfg, w, r, bf16_storage=True) for r in reqs]
+    trace = ru.Trace()
+    passes = {"": 96, "x": 96, "y": 200, "z": 200}     # every shape of a pass comes again in the next
+    for prefix, portion in passes.items():
+        ru.lockstep(trace, same, portion=portion, prefix=prefix)
+    ru.mixed(trace, reqs)
+    outs = {}
+    for graphs in (True, False):
+        out = ru.run_trace(model_dirs[name], dtype, trace, tmp_path / f"out{int(graphs)}",
+                           page_size=zu.CONFIGS[name]["page_size"], cuda_graphs=graphs,
+                           extra_env={"DIB200_GEMM_MAX_ROWS": "1000000", "DIB200_HEADS_LINEAR_ROWS": "1000000"})
+        outs[graphs] = ru.read_rows(out, trace, cfg["vocab"])
+    for key_pos, row in outs[True].items():
+        assert torch.equal(row, outs[False][key_pos]), key_pos
+    for (key, pos), row in outs[True].items():
+        i = int(key.lstrip("xyz")[1:])
+        scale = float(exact[i].std())
+        err = row_error(row, exact[i][pos])
+        yard = max(row_error(a, b) for a, b in zip(stored[i], exact[i]))
+        bound = 1e-4 * scale if dtype == "float32" else max(3.0 * yard, 2e-2 * scale)
+        assert err <= bound, f"{name}/{dtype}: request {key} position {pos}: {err:.4g} exceeds {bound:.4g}"
+
+
 @pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("name", ["z1", "z4"])
 def test_greedy_generation_through_the_entry_point(name, dtype, model_dirs):
