@@ -339,7 +339,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     const int r = warp * 16 + (lane >> 2) + rr * 8;
     const int tl = r / G, g = r % G;
     if (tl >= ntok) continue;
-    // a sink: exp(sink[head]) joins the denominator (no key, no value, not scaled)
+    // a sink: one more term exp(sink[head]) in the denominator, taken as it is, nothing in the output
     if (sink != nullptr) lrow[rr] += fast_exp2(sink[kvh * G + g] * LOG2E - mrow[rr]);
     const float inv = 1.0f / lrow[rr];
     const size_t t = (size_t)(q_begin + tok0 + tl);

@@ -406,7 +406,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
     sL[hf * 128 + r] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     float l_row = sL[r] + sL[128 + r];
-    // a sink: exp(sink[head]) joins the denominator (no key, no value, not scaled)
+    // a sink: one more term exp(sink[head]) in the denominator, taken as it is, nothing in the output
     if (sink != nullptr && valid) l_row += fast_exp2(sink[kvh * G + g] * LOG2E - m_ref);
     if (ok) {
       const float inv = 1.0f / l_row;

@@ -1197,7 +1197,7 @@ def masked_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float
     """[T, Hq, Dv]: softmax attention of every token of the step over the keys of its sequence in the
     paged cache that ``mask`` lets it see (a query at position p: "causal" 0 .. p; "window" p - size + 1
     .. p; "chunk" floor(p / size) * size .. p).  ``sink`` float32 [Hq]: the denominator also holds
-    exp(sink[h]) (no key, no value, not scaled).  ``gate`` [T, >= gate_col + Hq * Dv] (a tensor or split
+    exp(sink[h]) as one more term that brings nothing into the output and is taken as it is.  ``gate`` [T, >= gate_col + Hq * Dv] (a tensor or split
     sums): the output is multiplied by sigmoid(gate[t, gate_col + h * Dv + d]).  ``values_in_keys``: the
     cache holds keys only and a key's first Dv elements are its value."""
     _need(q, "q", None, 3)

@@ -8,7 +8,7 @@ the position encoding's rotation of the first ``rotary_dim`` elements of every q
 rest pass).  score = q . k * scale.  ``mask``: "causal" (every key up to the query), "window" (the
 last ``mask_size`` keys, the query's own included) or "chunk" (the keys of the query's own chunk of
 ``mask_size`` positions, chunks counted from position 0).  ``sink``: the softmax's denominator also
-holds exp(s_h), a learned number per head with no key and no value.  ``gate``: the concatenated
+holds one more term exp(s_h), s_h a learned number per head, that brings nothing into the output.  ``gate``: the concatenated
 heads are multiplied by sigmoid(W_g x) before the output projection.  Norms, angles, scores and the
 softmax are float32.
 """
