@@ -230,8 +230,8 @@ class ZatiraxConfig:
             enters = t if (t is not None and i == self.loop[0]) else None
             schedule.append(ScheduleEntry(layer=i, cache=cache_id, writes_cache=True, enter_vector=enters))
         looped = self.loop is not None and self.loop[1] > self.loop[0]
-        if self.loop is not None and not looped:
-            ignored.append("loop.step")
+        if not looped:
+            ignored.append("loop.step")       # (nothing is looped: the vectors, if stored, are not used)
         return ModelPlan(
             hidden_size=w, vocab_size=self.vocab,
             embedding=PartSpec("scaled_token_embedding", dict(name="embed", vocab_size=self.vocab, hidden_size=w,

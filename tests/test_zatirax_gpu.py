@@ -325,6 +325,7 @@ CASES = {       # configuration -> request lengths, seed
     "z2": ([5, 33, 64, 200], 32),
     "z3": ([3, 22, 57, 130, 333], 33),
     "z4": ([1, 9, 40, 150, 300], 34),
+    "z5": ([2, 31, 129, 420], 35),
 }
 
 
@@ -376,7 +377,7 @@ def test_replay_all_cuttings(name, dtype, model_dirs, plain_logits, tmp_path):
     print(f"{name}/{dtype}: worst difference {worst:.3e} of the logits' spread")
 
 
-@pytest.mark.parametrize("name, dtype", [("z4", "bfloat16"), ("z1", "bfloat16"), ("z3", "float32")])
+@pytest.mark.parametrize("name, dtype", [("z4", "bfloat16"), ("z3", "float32")])
 def test_replay_with_captured_graphs(name, dtype, model_dirs, tmp_path):
     """The step function as generation runs it: pure-decode steps and steps whose shape has come twice
     before are replayed as captured CUDA graphs, whose kernels size their grids and tile lists for the
@@ -385,13 +386,13 @@ def test_replay_with_captured_graphs(name, dtype, model_dirs, tmp_path):
     run of the same trace (equal bits: every product is kept on the kernels whose sums do not depend on
     the row count) and against the plain implementation."""
     cfg, w = pz.read_model_dir(model_dirs[name])
-    same = zu.requests(cfg["vocab"], [330] * 4, 41)
+    same = zu.requests(cfg["vocab"], [250] * 4, 41)
     other = zu.requests(cfg["vocab"], [33, 150, 77], 42)
     reqs = same + other
     exact = [pz.forward(cfg, w, r) for r in reqs]
     stored = [pz.forward(cfg, w, r, bf16_storage=True) for r in reqs]
     trace = ru.Trace()
-    passes = {"": 96, "x": 96, "y": 200, "z": 200}     # every shape of a pass comes again in the next
+    passes = {"": 96, "x": 96, "y": 96, "z": 200}      # every shape of a pass comes again in the next
     for prefix, portion in passes.items():
         ru.lockstep(trace, same, portion=portion, prefix=prefix)
     ru.mixed(trace, reqs)

@@ -59,6 +59,16 @@ CONFIGS = {
         "layers": [attention(4, 2, 64, 64, 72, 32, 10000.0, scaling=(8.0, 1.0, 4.0, 64), ff=192, limit=1.0),
                    latent(4, 32, 32, 32, 64, 41, 10000.0, ff=192, limit=1.0),
                    attention(2, 2, 128, 128, 100, 64, 500.0, ff=None)]}),
+    # five layers in another order, a loop over the middle three, grouped heads on the tensor-core kernels,
+    # windows and chunks of whole pages
+    "z5": dict(page_size=16, seed=45, config={
+        "architecture": "Zatirax", "vocab": 512, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 10.0},
+        "loop": {"start": 1, "stop": 4, "times": 2},
+        "layers": [latent(8, 32, 16, 32, 128, 64, 30000.0, ff=384, limit=1.0),
+                   attention(8, 2, 64, 64, 128, 32, 10000.0, scaling=(8.0, 1.0, 4.0, 256), ff=384, limit=2.0),
+                   attention(8, 4, 64, 64, 64, 16, 40000.0, ff=None),
+                   latent(4, 64, 32, 64, 64, 128, 10000.0, ff=256, limit=0.8),
+                   attention(4, 4, 128, 128, 96, 32, 20000.0, scaling=(4.0, 1.0, 2.0, 128), ff=384, limit=1.0)]}),
 }
 
 
