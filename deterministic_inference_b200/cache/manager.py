@@ -75,6 +75,9 @@ class PageGroup:
         self.free: list[int] = list(range(num_pages - 1, 0, -1))
         self.held: set[int] = set()
         self.pages: list[list[int]] = [[] for _ in range(max_reqs)]
+        # per slot: the pages before this index (the kept first ones aside) have been given back, so the
+        # next look starts there instead of walking the released run again every step
+        self.first_live: list[int] = [0] * max_reqs
         self.pool: Optional[torch.Tensor] = None
 
     @property
@@ -114,20 +117,21 @@ class PageGroup:
         n = 0
         pl = self.pages[slot]
         kept = -(-self.keep_first // self.page_size)     # pages that hold a kept position
-        for i in range(kept, len(pl)):
-            if (i + 1) * self.page_size <= first_needed:
-                if pl[i] != NULL_PAGE:
-                    self._give_back(pl[i])
-                    pl[i] = NULL_PAGE
-                    n += 1
-            else:
-                break
+        i = max(kept, self.first_live[slot])
+        while i < len(pl) and (i + 1) * self.page_size <= first_needed:
+            if pl[i] != NULL_PAGE:
+                self._give_back(pl[i])
+                pl[i] = NULL_PAGE
+                n += 1
+            i += 1
+        self.first_live[slot] = i
         return n
 
     def release_all(self, slot: int) -> None:
         for p in self.pages[slot]:
             self._give_back(p)
         self.pages[slot] = []
+        self.first_live[slot] = 0
 
 
 class StateGroup:

@@ -245,7 +245,10 @@ def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, gr
                 continue
             pl = g.pages[e.slot]
             m = min(len(pl), lay.width)
-            bt[bi, :m] = pl[:m]
+            # (a group that gives pages back and keeps no first keys: the run of given-back pages at the
+            # front stays the zeros the array was filled with)
+            f = min(g.first_live[e.slot], m) if (g.window is not None and not g.keep_first) else 0
+            bt[bi, f:m] = pl[f:m]
             q = q_lens[bi]
             if q == 1:
                 page = pl[e.num_computed // ps]
